@@ -1,0 +1,132 @@
+/*
+ * libtessel_b200 - C ABI.
+ *
+ * A drop-in for the launch path of the tessel LLM engine: everything
+ * src/llm/engine.rs does on a device goes through `Gpu` (src/gpu.rs:28-263),
+ * and each entry point below stands where one method of `Gpu` stands. The
+ * kernels behind `tb200_kernel` are hand-written sm_100a CUDA, compiled ahead
+ * of time; there is no JIT and no CPU path. All functions return 0 on success
+ * and a non-zero code on failure, with the text (CUDA error number and string
+ * included, as src/driver.rs:181-195 formats it) available from
+ * `tb200_last_error`. Nothing throws or aborts across this boundary.
+ *
+ * One context drives one device on one stream, from one thread at a time
+ * (the contract of src/runtime.rs:48-52). A tensor-parallel run is one process
+ * and one context per GPU.
+ *
+ * Device memory is addressed by plain 64-bit device pointers; buffers from
+ * `tb200_alloc` and buffers allocated elsewhere (another CUDA library in the
+ * same process) are both accepted by every call.
+ */
+#ifndef TESSEL_B200_H
+#define TESSEL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tb200_ctx tb200_ctx;
+typedef int32_t tb200_op;    /* a kernel specialised for its shapes: `K` of src/gpu.rs:48 */
+typedef int32_t tb200_graph; /* a recorded step: `GraphExec` of src/driver.rs */
+
+/* Gpu::new (src/gpu.rs:53-67) + Cuda::new (src/driver.rs:150-175): binds
+ * `device`, creates the stream. Fails if the device is not compute capability
+ * 10.x. */
+int tb200_init(int device, tb200_ctx** out);
+void tb200_destroy(tb200_ctx* ctx);
+
+/* The message of the last failed call on `ctx` (NULL: of the last failed
+ * tb200_init). Valid until the next call on the same context. */
+const char* tb200_last_error(tb200_ctx* ctx);
+
+/* Gpu::alloc (src/gpu.rs:70-85): `bytes` of device memory, zero-filled. */
+int tb200_alloc(tb200_ctx* ctx, size_t bytes, uint64_t* dptr);
+/* The reference never frees (process lifetime); offered for long-lived hosts. */
+int tb200_free(tb200_ctx* ctx, uint64_t dptr);
+
+/* Gpu::write (src/gpu.rs:88-107): synchronous host-to-device copy at byte
+ * `offset`; bounds-checked against the allocation when `dptr` came from
+ * tb200_alloc. */
+int tb200_write(tb200_ctx* ctx, uint64_t dptr, size_t offset, const void* src, size_t bytes);
+/* Asynchronous variant on the context's stream; `src` must stay valid (and
+ * should be pinned) until the next tb200_sync. */
+int tb200_write_async(tb200_ctx* ctx, uint64_t dptr, size_t offset, const void* src, size_t bytes);
+
+/* Gpu::read (src/gpu.rs:110-131): waits for the stream, then copies
+ * device-to-host. */
+int tb200_read(tb200_ctx* ctx, uint64_t dptr, size_t offset, void* dst, size_t bytes);
+
+/* No counterpart in the reference (its host buffers are pageable Vec<u8>):
+ * page-locked host memory, so that tb200_write_async / tb200_read move data at
+ * full PCIe speed and asynchronously. */
+int tb200_host_alloc(tb200_ctx* ctx, size_t bytes, void** out);
+int tb200_host_free(tb200_ctx* ctx, void* ptr);
+
+/* Gpu::kernel (src/gpu.rs:148-172): the kernel `name` for these array shapes,
+ * made once and cached. `shapes` holds the dimensions of every array
+ * parameter back to back, in the kernel's parameter order (kernels/llm.tl),
+ * `ranks[i]` the number of dimensions of array i. Names: embed, rmsnorm,
+ * linear, linear_residual, logits, gate_up, rope_q, kv_write,
+ * prefill_attention, decode_attention, rmsnorm_rows (kernels/llm.tl:10-182),
+ * matmul (kernels/matmul.tl:3-17), flash_attention, paged_attention
+ * (kernels/attention.tl:4-51); and, with no counterpart in the reference,
+ * linear_f32 (X[M,K], W[N,K], Y f32[M,N]), residual_add (R f32[M,N], P
+ * f32[M,N]) and argmax_rows (X f32[M,N], out i32[M]). The reference's `meta`
+ * and `warps` arguments have no equivalent: tile shapes are chosen inside. */
+int tb200_kernel(tb200_ctx* ctx, const char* name, const int64_t* shapes, const int32_t* ranks, int n_arrays,
+                 tb200_op* out);
+
+/* Gpu::launch (src/gpu.rs:179-217): asynchronous launch on the context's
+ * stream. `args[i]` is a device pointer for an array parameter, or the bits of
+ * an f32/i32 scalar in the low 32 bits (src/gpu.rs:192-193), in the kernel's
+ * parameter order. */
+int tb200_launch(tb200_ctx* ctx, tb200_op op, const uint64_t* args, int n_args);
+
+/* Gpu::capture_begin / capture_end / replay (src/gpu.rs:233-247). */
+int tb200_capture_begin(tb200_ctx* ctx);
+int tb200_capture_end(tb200_ctx* ctx, tb200_graph* out);
+int tb200_replay(tb200_ctx* ctx, tb200_graph graph);
+
+/* Gpu::sync (src/gpu.rs:249-254). Also reports a kernel whose bounded wait
+ * ran out since the last sync. */
+int tb200_sync(tb200_ctx* ctx);
+
+/* Cuda::time (src/driver.rs:366-380), split in two: events on the context's
+ * stream around whatever is launched in between; `ms` is device time. */
+int tb200_time_begin(tb200_ctx* ctx);
+int tb200_time_end(tb200_ctx* ctx, float* ms);
+
+/* Gpu::launches (src/gpu.rs:37): kernels launched through this context
+ * (a replayed graph counts every kernel it holds). */
+int tb200_launch_count(tb200_ctx* ctx, uint64_t* out);
+
+/* No counterpart in the reference: run on a stream the host already owns
+ * (a `cudaStream_t`), so that other libraries' work can be ordered with the
+ * kernels. NULL restores the context's own stream. */
+int tb200_set_stream(tb200_ctx* ctx, void* cuda_stream);
+/* The stream in use, as a `cudaStream_t`. */
+int tb200_get_stream(tb200_ctx* ctx, void** cuda_stream);
+
+/* Tensor parallelism (the reference has none: src/driver.rs:154 takes device
+ * 0 only). One process per GPU: rank 0 obtains an id, the host hands it to the
+ * other ranks, every rank joins, and tb200_allreduce sums `count` elements in
+ * place across ranks on the context's stream (NCCL over NVLink). dtype: 0 =
+ * f32, 1 = f16. */
+#define TB200_COMM_ID_BYTES 128
+int tb200_comm_id(tb200_ctx* ctx, void* id_out);
+int tb200_comm_init(tb200_ctx* ctx, int rank, int nranks, const void* id);
+int tb200_allreduce(tb200_ctx* ctx, uint64_t dptr, size_t count, int dtype);
+
+/* Host helper: the seeded xorshift generator of src/bench.rs:13-35, as
+ * Weights::random (src/llm/mod.rs:80-108) draws from it. `state` starts as
+ * tb200_rng_seed(seed). */
+uint64_t tb200_rng_seed(uint64_t seed);
+void tb200_rng_uniform(uint64_t* state, float* out, size_t n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TESSEL_B200_H */

@@ -1,0 +1,294 @@
+// Shared declarations of libtessel_b200: the context behind the C ABI, the op
+// table, and the sm_100a PTX wrappers (mbarrier, TMA, tcgen05/TMEM) the kernels
+// are written with.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace tb {
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+
+enum Kind : int {
+  K_EMBED = 0,
+  K_RMSNORM,
+  K_LINEAR,
+  K_LINEAR_RESIDUAL,
+  K_LOGITS,
+  K_GATE_UP,
+  K_ROPE_Q,
+  K_KV_WRITE,
+  K_PREFILL_ATTENTION,
+  K_DECODE_ATTENTION,
+  K_RMSNORM_ROWS,
+  K_MATMUL,
+  K_FLASH_ATTENTION,
+  K_PAGED_ATTENTION,
+  // Extensions beyond the reference's kernel list.
+  K_LINEAR_F32,     // Y f32 = X W^T (a tensor-parallel rank's partial product)
+  K_RESIDUAL_ADD,   // R f32 += P f32
+  K_ARGMAX_ROWS,    // first index of each row's maximum
+  K_COUNT
+};
+
+struct Op {
+  Kind kind;
+  std::string name;
+  std::vector<std::vector<int64_t>> shapes;
+  int n_args = 0;
+  // Scratch owned by the op (global memory beyond inputs and outputs), sized
+  // when the op is made so that a launch allocates nothing.
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  // Kernel-specific tuning chosen when the op is made.
+  int p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+};
+
+struct Ctx {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = true;
+  std::string err;
+  std::map<uint64_t, size_t> allocs;  // device pointer -> bytes, for bounds checks
+  std::vector<Op> ops;
+  std::unordered_map<std::string, int> op_by_key;
+  std::vector<cudaGraphExec_t> graphs;
+  std::vector<size_t> graph_nodes;  // kernels each recorded graph holds
+  bool capturing = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  uint64_t launches = 0;
+  // Device word the kernels raise when a bounded wait runs out: 0 = healthy.
+  unsigned int* status = nullptr;
+  // cuTensorMapEncodeTiled, resolved through the runtime (no link to libcuda).
+  void* encode_tiled = nullptr;
+  // Tensor-parallel communicator (NCCL, loaded at run time), or null.
+  void* nccl_lib = nullptr;
+  void* comm = nullptr;
+  int rank = 0, nranks = 1;
+};
+
+int fail(Ctx* c, const std::string& msg);
+int cuda_fail(Ctx* c, cudaError_t e, const char* what);
+
+#define TB_CUDA(c, expr)                                      \
+  do {                                                        \
+    cudaError_t e__ = (expr);                                 \
+    if (e__ != cudaSuccess) return cuda_fail((c), e__, #expr); \
+  } while (0)
+
+// A tiled tensor map over a row-major array of `rank` dims (dims[0] innermost).
+// strides_bytes[i] is the stride of dims[i+1]. Returns 0 on success.
+int make_tensor_map(Ctx* c, CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz);
+
+// Launchers, one per kernel family. `a` holds the launch arguments as the C
+// ABI received them: device pointers, or scalar bits in the low 32 bits.
+int make_glue(Ctx* c, Op& op);
+int launch_glue(Ctx* c, Op& op, const uint64_t* a);
+int make_gemm(Ctx* c, Op& op);
+int launch_gemm(Ctx* c, Op& op, const uint64_t* a);
+int make_decode(Ctx* c, Op& op);
+int launch_decode(Ctx* c, Op& op, const uint64_t* a);
+int make_prefill(Ctx* c, Op& op);
+int launch_prefill(Ctx* c, Op& op, const uint64_t* a);
+
+inline float bits_f32(uint64_t v) {
+  uint32_t u = (uint32_t)v;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+// ---------------------------------------------------------------------------
+// Device side
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// Waits give up after this many nanoseconds, raise the status word and let the
+// kernel run to its end (results are then garbage, the context stays usable).
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait on an mbarrier phase. On time-out the global status word gets
+// `code` and every later wait of the grid returns at once.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int code) {
+  if (mbar_try(bar, parity)) return;
+  const unsigned long long t0 = globaltimer();
+  unsigned int spins = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++spins & 1023u) == 0) {
+      if (*(volatile unsigned int*)status != 0) return;
+      if (globaltimer() - t0 > WAIT_LIMIT_NS) {
+        atomicCAS(status, 0u, code);
+        return;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)m) : "memory");
+}
+
+// TMA tile loads into this CTA's shared memory, completion on an mbarrier.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(dst)),
+      "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z,
+                                            int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], "
+      "[%2];" ::"r"(smem_u32(dst)),
+      "l"((uint64_t)m), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+
+// ---- tcgen05 / TMEM ---------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot_in_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] * B[smem], f16 inputs, f32 accumulation, one CTA.
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrives on `bar` once every tcgen05.mma issued so far by this thread is done.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// 32 lanes x 32 columns of f32 from TMEM: thread i of the warp gets lane
+// (base lane + i), registers r[0..31] are consecutive columns.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format, version 1), 128-byte swizzle.
+// K-major tiles: rows of 128 bytes, 8-row groups `sbo` bytes apart.
+// MN-major tiles: 64-element blocks `lbo` bytes apart, 8-k groups `sbo` apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16: f16 A and B, f32 D, M x N tile.
+// b_mn = 1 when B is stored N-major (a [K,N] row-major operand).
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int M, int N, int a_mn, int b_mn) {
+  return (1u << 4)                      // D format f32
+         | (0u << 7) | (0u << 10)       // A, B format f16
+         | ((uint32_t)a_mn << 15) | ((uint32_t)b_mn << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// Packs two f32 into f16x2 (round to nearest even), low half = a.
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace tb

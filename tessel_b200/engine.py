@@ -1,0 +1,326 @@
+"""The model on the device: weights, the paged KV cache, activation buffers for
+the largest step, and one step of the decoder as a sequence of kernel launches.
+
+Host-side mirror of tessel's ``src/llm/engine.rs``: ``Limits`` (:21-32),
+``Attn`` (:35-45), ``padded`` (:94-98), ``Engine::new`` (:150-226),
+``Engine::step`` (:275-354) and ``Engine::launch_all`` (:359-529), with the
+same padding rules, buffer dtypes and launch order, driving
+``libtessel_b200`` through :class:`tessel_b200.gpu.Gpu`.
+
+Beyond the reference: the step's integer inputs go up from page-locked memory
+in asynchronous copies; ``step_greedy`` picks the tokens on the device so that
+only ``len(want)`` integers come back instead of ``len(want) * vocab`` floats;
+and the model can be tensor-parallel (``rank``/``nranks``): attention and KV
+heads and the MLP columns are sharded, o_proj and down_proj produce f32
+partials that are summed across ranks (one allreduce each) before they are
+added to the residual stream.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from .gpu import Buf, F32, Gpu, K
+from .model import Config, Weights, rope_tables
+
+
+@dataclass
+class Limits:
+    """Engine limits (src/llm/engine.rs:21-32)."""
+    page: int           # tokens per cache page
+    pages: int          # pages in the cache (shared by all sequences)
+    max_tokens: int     # most tokens in one step (a prompt, or a batch of decodes)
+    max_seq_pages: int  # most pages one sequence holds
+
+
+class Prefill:
+    """One sequence's prompt from position 0: causal over the step's tokens."""
+
+
+@dataclass
+class Packed:
+    """Several prompts packed into the step: row r belongs to the sequence whose first row is starts[r]."""
+    starts: Sequence[int]
+
+
+@dataclass
+class Decode:
+    """One token per sequence against its cache: page tables and lengths (including the token itself)."""
+    tables: Sequence[Sequence[int]]
+    lens: Sequence[int]
+
+
+def padded(n: int) -> int:
+    """Rows a step is made for: at least 16, rounded up to a power of two (src/llm/engine.rs:94-98)."""
+    n = max(n, 16)
+    return 1 << (n - 1).bit_length()
+
+
+def shard_weights(w: Weights, rank: int, nranks: int) -> Weights:
+    """Rank ``rank``'s slice of the model under ``nranks``-way tensor parallelism.
+
+    Query heads, KV heads and MLP columns are split evenly: the three row
+    blocks of wqkv are sliced separately, wo and wd keep the matching input
+    columns. Norms, embedding and LM head are replicated.
+    """
+    from .model import Layer
+    cfg = w.cfg
+    if nranks == 1:
+        return w
+    if cfg.heads % nranks or cfg.kv_heads % nranks or cfg.ffn % nranks:
+        raise ValueError(f"heads {cfg.heads}, kv_heads {cfg.kv_heads} and ffn {cfg.ffn} must divide by {nranks}")
+    hd, H, G = cfg.head_dim, cfg.heads, cfg.kv_heads
+    hl, gl, fl = H // nranks, G // nranks, cfg.ffn // nranks
+    local = Config(**{**cfg.__dict__, "heads": hl, "kv_heads": gl, "ffn": fl})
+    layers = []
+    for l in w.layers:
+        q = l.wqkv[rank * hl * hd:(rank + 1) * hl * hd]
+        k = l.wqkv[H * hd + rank * gl * hd:H * hd + (rank + 1) * gl * hd]
+        v = l.wqkv[(H + G) * hd + rank * gl * hd:(H + G) * hd + (rank + 1) * gl * hd]
+        layers.append(Layer(
+            attn_norm=l.attn_norm, wqkv=np.ascontiguousarray(np.concatenate([q, k, v], 0)),
+            wo=np.ascontiguousarray(l.wo[:, rank * hl * hd:(rank + 1) * hl * hd]), mlp_norm=l.mlp_norm,
+            wg=np.ascontiguousarray(l.wg[rank * fl:(rank + 1) * fl]),
+            wu=np.ascontiguousarray(l.wu[rank * fl:(rank + 1) * fl]),
+            wd=np.ascontiguousarray(l.wd[:, rank * fl:(rank + 1) * fl])))
+    return Weights(local, w.embed, layers, w.norm, w.lm_head)
+
+
+@dataclass
+class _DevLayer:
+    n1: Buf
+    wqkv: Buf
+    wo: Buf
+    n2: Buf
+    wg: Buf
+    wu: Buf
+    wd: Buf
+    kc: Buf
+    vc: Buf
+
+
+class Engine:
+    """``w`` holds the full model; with ``nranks > 1`` this engine keeps rank ``rank``'s shard of it."""
+
+    def __init__(self, gpu: Gpu, w: Weights, lim: Limits, rank: int = 0, nranks: int = 1):
+        full = w.cfg
+        if full.heads % full.kv_heads or full.head_dim % 2:
+            raise ValueError("heads must be a multiple of kv_heads, head_dim even")
+        w = shard_weights(w, rank, nranks)
+        cfg = w.cfg
+        self.gpu = gpu
+        self.cfg = cfg
+        self.full_cfg = full
+        self.lim = lim
+        self.rank, self.nranks = rank, nranks
+        # Replay decode steps as CUDA graphs (one launch instead of hundreds).
+        self.graphs = True
+        self._graph: Dict[tuple, int] = {}
+        up = gpu.tensor
+        self.embed = up(w.embed)
+        self.head = up(w.lm_head) if w.lm_head is not None else self.embed
+        self.norm = up(w.norm)
+        slots = lim.pages * lim.page
+        kv_bytes = slots * cfg.kv_heads * cfg.head_dim * 2
+        self.layers: List[_DevLayer] = []
+        for l in w.layers:
+            self.layers.append(_DevLayer(up(l.attn_norm), up(l.wqkv), up(l.wo), up(l.mlp_norm), up(l.wg), up(l.wu),
+                                         up(l.wd), gpu.alloc(kv_bytes), gpu.alloc(kv_bytes)))
+        c, s = rope_tables(cfg)
+        self.cos, self.sin = up(c), up(s)
+        t = padded(lim.max_tokens)
+        self.tmax = t
+        hd, gd = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        a = gpu.alloc
+        self.x = a(t * cfg.dim * 4)
+        self.h = a(t * cfg.dim * 2)
+        self.qkv = a(t * cfg.qkv() * 2)
+        self.q = a(t * hd * 2)
+        self.k = a(t * gd * 2)
+        self.v = a(t * gd * 2)
+        self.o = a(t * hd * 2)
+        self.mlp = a(t * cfg.ffn * 2)
+        self.last = a(t * cfg.dim * 2)
+        self.logits = a(t * cfg.vocab * 4)
+        self.part = a(t * cfg.dim * 4) if nranks > 1 else None  # a rank's partial o_proj / down_proj
+        self.tok, self.pos, self.slot, self.idx = a(t * 4), a(t * 4), a(t * 4), a(t * 4)
+        self.table = a(t * lim.max_seq_pages * 4)
+        self.lens, self.starts = a(t * 4), a(t * 4)
+        self.picked = a(t * 4)
+        # Page-locked staging for a step's inputs and results.
+        mp = lim.max_seq_pages
+        self._stage = gpu.host_array((6 * t + t * mp,), np.int32)
+        self._picked_host = gpu.host_array((t,), np.int32)
+        self._logits_host: Optional[np.ndarray] = None
+
+    # -- one step ----------------------------------------------------------------
+    def _upload(self, tokens, pos, slots, attn, want):
+        """Pads the step's integer inputs and sends them up. Returns (n, t, bw, prefill)."""
+        n = len(tokens)
+        if n == 0 or n > self.lim.max_tokens or len(pos) != n or len(slots) != n:
+            raise ValueError(f"a step of {n} tokens (at most {self.lim.max_tokens})")
+        t = padded(n)
+        ns = self.lim.pages * self.lim.page
+        mp = self.lim.max_seq_pages
+        T = self.tmax
+        st = self._stage
+        g = self.gpu
+        # Inputs, padded: token 0 at position 0, writing to no slot.
+        tk, ps, sl = st[0:t], st[T:T + t], st[2 * T:2 * T + t]
+        tk[:n], tk[n:] = tokens, 0
+        ps[:n], ps[n:] = pos, 0
+        sl[:n], sl[n:] = slots, ns
+        g.write_async(self.tok, 0, tk)
+        g.write_async(self.pos, 0, ps)
+        g.write_async(self.slot, 0, sl)
+        prefill = not isinstance(attn, Decode)
+        if prefill:
+            # Where each row's sequence begins (padding rows: at themselves).
+            sr = st[5 * T:5 * T + t]
+            if isinstance(attn, Packed):
+                if len(attn.starts) != n:
+                    raise ValueError("packed prefill: one start per token")
+                sr[:n] = attn.starts
+            else:
+                sr[:n] = 0
+            sr[n:] = np.arange(n, t, dtype=np.int32)
+            g.write_async(self.starts, 0, sr)
+        else:
+            tb = st[6 * T:6 * T + t * mp].reshape(t, mp)
+            ln = st[4 * T:4 * T + t]
+            tb[:] = 0
+            ln[:] = 0
+            for b, row in enumerate(attn.tables):
+                tb[b, :len(row)] = row
+            ln[:len(attn.lens)] = attn.lens
+            g.write_async(self.table, 0, tb)
+            g.write_async(self.lens, 0, ln)
+        # Rows whose logits are wanted.
+        bw = padded(len(want)) if len(want) else None
+        if bw is not None:
+            ix = st[3 * T:3 * T + bw]
+            ix[:len(want)] = want
+            ix[len(want):] = 0
+            g.write_async(self.idx, 0, ix)
+        return n, t, bw, prefill
+
+    def _run(self, t: int, prefill: bool, bw: Optional[int], greedy: bool) -> None:
+        g = self.gpu
+        g.phase = "prefill" if prefill else "decode"
+        # Profiling times every launch on its own, so it runs without graphs.
+        if (not prefill) and self.graphs and g.profile is None and bw == t:
+            # A decode step of this size: replay its recorded launches, or run
+            # them and record them for the next time.
+            key = (t, greedy)
+            if key in self._graph:
+                g.replay(self._graph[key])
+            else:
+                self.launch_all(t, False, bw, greedy)
+                g.sync()
+                g.capture_begin()
+                try:
+                    self.launch_all(t, False, bw, greedy)
+                finally:
+                    gr = g.capture_end()
+                self._graph[key] = gr
+        else:
+            self.launch_all(t, prefill, bw, greedy)
+
+    def step(self, tokens, pos, slots, attn, want: Sequence[int]) -> np.ndarray:
+        """Runs the decoder over ``tokens`` at positions ``pos``, writing their keys and values
+        to cache slots ``slots``, and returns the logits of the rows in ``want``: f32
+        ``[len(want), vocab]`` (a view of page-locked memory, valid until the next step)."""
+        n, t, bw, prefill = self._upload(tokens, pos, slots, attn, want)
+        self._run(t, prefill, bw, False)
+        if not len(want):
+            self.gpu.sync()
+            return np.empty((0, self.cfg.vocab), np.float32)
+        v = self.cfg.vocab
+        if self._logits_host is None or self._logits_host.shape[0] < len(want):
+            self._logits_host = self.gpu.host_array((padded(len(want)), v), np.float32)
+        out = self._logits_host[:len(want)]
+        self.gpu.read(self.logits, 0, out)
+        return out
+
+    def step_greedy(self, tokens, pos, slots, attn, want: Sequence[int]) -> np.ndarray:
+        """As ``step``, but the first-maximum choice of src/llm/mod.rs:132-140 is made on the
+        device: returns int32 ``[len(want)]`` token ids."""
+        n, t, bw, prefill = self._upload(tokens, pos, slots, attn, want)
+        self._run(t, prefill, bw, True)
+        if not len(want):
+            self.gpu.sync()
+            return np.empty((0,), np.int32)
+        out = self._picked_host[:len(want)]
+        self.gpu.read(self.picked, 0, out)
+        return out
+
+    # -- the launch sequence -------------------------------------------------------
+    def launch_all(self, t: int, prefill: bool, bw: Optional[int], greedy: bool = False) -> None:
+        """Launches one step's kernels for ``t`` rows: the decoder, then, for ``bw`` rows of
+        logits, the final norm and the LM head (and the token choice when ``greedy``)."""
+        cfg, lim, g = self.cfg, self.lim, self.gpu
+        dm, nh, ng, hd = cfg.dim, cfg.heads, cfg.kv_heads, cfg.head_dim
+        w, f, v = cfg.qkv(), cfg.ffn, cfg.vocab
+        ns, mp, npos = lim.pages * lim.page, lim.max_seq_pages, cfg.max_pos
+        scale = F32(1.0 / math.sqrt(hd))
+        eps = F32(cfg.eps)
+        tp = self.nranks > 1
+        k = g.kernel
+        embed = k("embed", [[t], [v, dm], [t, dm]])
+        norm = k("rmsnorm", [[t, dm], [dm], [t, dm]])
+        qkv = k("linear", [[t, dm], [w, dm], [t, w]])
+        rope = k("rope_q", [[t, w], [t], [npos, hd // 2], [npos, hd // 2], [t, nh, hd]])
+        kvw = k("kv_write", [[t, w], [t], [t], [npos, hd // 2], [npos, hd // 2], [ns, ng, hd], [ns, ng, hd],
+                             [t, ng, hd], [t, ng, hd]])
+        if prefill:
+            att = k("prefill_attention", [[t, nh, hd], [t, ng, hd], [t, ng, hd], [t], [t, nh, hd]])
+        else:
+            att = k("decode_attention", [[t, nh, hd], [lim.pages, lim.page, ng, hd], [lim.pages, lim.page, ng, hd],
+                                         [t, mp], [t], [t, nh, hd]])
+        proj = "linear_f32" if tp else "linear_residual"
+        oproj = k(proj, [[t, nh * hd], [dm, nh * hd], [t, dm]])
+        gu = k("gate_up", [[t, dm], [f, dm], [f, dm], [t, f]])
+        down = k(proj, [[t, f], [dm, f], [t, dm]])
+        radd = k("residual_add", [[t, dm], [t, dm]]) if tp else None
+
+        def project(kern: K, x: Buf, wt: Buf) -> None:
+            if not tp:
+                g.launch(kern, [x, wt, self.x])
+                return
+            g.launch(kern, [x, wt, self.part])
+            g.allreduce(self.part, t * dm, 0)
+            g.launch(radd, [self.x, self.part])
+
+        g.launch(embed, [self.tok, self.embed, self.x])
+        for l in self.layers:
+            g.launch(norm, [self.x, l.n1, self.h, eps])
+            g.launch(qkv, [self.h, l.wqkv, self.qkv])
+            g.launch(rope, [self.qkv, self.pos, self.cos, self.sin, self.q])
+            g.launch(kvw, [self.qkv, self.pos, self.slot, self.cos, self.sin, l.kc, l.vc, self.k, self.v])
+            if prefill:
+                g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
+            else:
+                g.launch(att, [self.q, l.kc, l.vc, self.table, self.lens, self.o, scale])
+            project(oproj, self.o, l.wo)
+            g.launch(norm, [self.x, l.n2, self.h, eps])
+            g.launch(gu, [self.h, l.wg, l.wu, self.mlp])
+            project(down, self.mlp, l.wd)
+        if bw is None:
+            return
+        fin = k("rmsnorm_rows", [[t, dm], [bw], [dm], [bw, dm]])
+        head = k("logits", [[bw, dm], [v, dm], [bw, v]])
+        g.launch(fin, [self.x, self.idx, self.norm, self.last, eps])
+        g.launch(head, [self.last, self.head, self.logits])
+        if greedy:
+            pick = k("argmax_rows", [[bw, v], [bw]])
+            g.launch(pick, [self.logits, self.picked])
+
+    # -- inspection (tests, parity checks) ------------------------------------------
+    def read_cache(self, layer: int):
+        """The K and V caches of one layer as f16 ``[pages, page, kv_heads, head_dim]`` arrays."""
+        shape = (self.lim.pages, self.lim.page, self.cfg.kv_heads, self.cfg.head_dim)
+        l = self.layers[layer]
+        return self.gpu.fetch(l.kc, np.float16, shape), self.gpu.fetch(l.vc, np.float16, shape)

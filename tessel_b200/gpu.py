@@ -1,0 +1,239 @@
+"""Buffers that outlive a kernel launch, and launches that take them.
+
+The host-side mirror of tessel's ``Gpu`` (src/gpu.rs:28-263), with the same
+methods, argument meaning and error behaviour, over the C ABI of
+``libtessel_b200``: ``alloc`` (zero-filled), ``write`` / ``read`` (bounds
+checked, synchronous), ``kernel`` (cached by name and shapes), ``launch``
+(asynchronous; buffers, f32 and i32 scalars), ``capture_begin`` /
+``capture_end`` / ``replay``, ``sync`` and the per-kernel ``profile``. Errors
+are raised as :class:`GpuError` carrying the library's message, where the
+reference returns ``Err(String)``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import struct
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+
+from . import _lib
+
+
+class GpuError(RuntimeError):
+    pass
+
+
+@dataclass(frozen=True)
+class Buf:
+    """A device buffer: its address and size in bytes (src/gpu.rs:14-19)."""
+    ptr: int
+    bytes: int
+
+
+@dataclass(frozen=True)
+class F32:
+    value: float
+
+
+@dataclass(frozen=True)
+class I32:
+    value: int
+
+
+Arg = Union[Buf, F32, I32]
+
+
+@dataclass(frozen=True)
+class K:
+    """A kernel made for its shapes (src/gpu.rs:47-48)."""
+    id: int
+    name: str
+
+
+def _bits(a: Arg) -> int:
+    if isinstance(a, Buf):
+        return a.ptr
+    if isinstance(a, F32):
+        return struct.unpack("<I", struct.pack("<f", a.value))[0]
+    if isinstance(a, I32):
+        return a.value & 0xFFFFFFFF
+    raise TypeError(f"not a kernel argument: {a!r}")
+
+
+class Gpu:
+    def __init__(self, device: int = 0):
+        self._l = _lib.lib()
+        h = C.c_void_p()
+        if self._l.tb200_init(device, C.byref(h)) != 0:
+            raise GpuError(self._l.tb200_last_error(None).decode())
+        self._h = h
+        self.device = device
+        self.launches = 0
+        # When set, every launch waits for its kernel and adds its time here,
+        # by (phase, kernel): [launches, milliseconds] (src/gpu.rs:38-40).
+        self.profile: Optional[Dict[Tuple[str, str], List[float]]] = None
+        self.phase = ""
+        self._names: Dict[int, str] = {}
+
+    # -- plumbing --------------------------------------------------------------
+    def _check(self, rc: int) -> None:
+        if rc != 0:
+            raise GpuError(self._l.tb200_last_error(self._h).decode())
+
+    def close(self) -> None:
+        if self._h:
+            self._l.tb200_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- buffers ---------------------------------------------------------------
+    def alloc(self, nbytes: int) -> Buf:
+        """A zeroed buffer of ``nbytes`` bytes."""
+        p = C.c_uint64()
+        self._check(self._l.tb200_alloc(self._h, nbytes, C.byref(p)))
+        return Buf(p.value, nbytes)
+
+    def wrap(self, ptr: int, nbytes: int) -> Buf:
+        """A buffer over device memory allocated elsewhere in this process."""
+        return Buf(int(ptr), int(nbytes))
+
+    def free(self, b: Buf) -> None:
+        self._check(self._l.tb200_free(self._h, b.ptr))
+
+    def write(self, b: Buf, offset: int, data) -> None:
+        """Copies ``data`` (bytes or a contiguous numpy array) into ``b`` at byte ``offset``."""
+        a = np.ascontiguousarray(data) if isinstance(data, np.ndarray) else np.frombuffer(bytes(data), np.uint8)
+        n = a.nbytes
+        if offset + n > b.bytes:
+            raise GpuError(f"write of {n} bytes at {offset} into a buffer of {b.bytes}")
+        self._check(self._l.tb200_write(self._h, b.ptr, offset, a.ctypes.data_as(C.c_void_p), n))
+
+    def write_async(self, b: Buf, offset: int, a: np.ndarray) -> None:
+        """As ``write`` without waiting; ``a`` must stay alive and unchanged until the next ``sync``."""
+        n = a.nbytes
+        if offset + n > b.bytes:
+            raise GpuError(f"write of {n} bytes at {offset} into a buffer of {b.bytes}")
+        self._check(self._l.tb200_write_async(self._h, b.ptr, offset, a.ctypes.data_as(C.c_void_p), n))
+
+    def read(self, b: Buf, offset: int, out: np.ndarray) -> np.ndarray:
+        """Reads ``out.nbytes`` bytes of ``b`` from byte ``offset`` (waiting for the GPU)."""
+        assert out.flags["C_CONTIGUOUS"]
+        if offset + out.nbytes > b.bytes:
+            raise GpuError(f"read of {out.nbytes} bytes at {offset} from a buffer of {b.bytes}")
+        self._check(self._l.tb200_read(self._h, b.ptr, offset, out.ctypes.data_as(C.c_void_p), out.nbytes))
+        return out
+
+    def read_f32(self, b: Buf, offset_elems: int, n: int) -> np.ndarray:
+        return self.read(b, offset_elems * 4, np.empty(n, np.float32))
+
+    def host_array(self, shape, dtype) -> np.ndarray:
+        """A page-locked numpy array (lives until the context is closed)."""
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        self._check(self._l.tb200_host_alloc(self._h, max(n, 1), C.byref(p)))
+        raw = (C.c_uint8 * max(n, 1)).from_address(p.value)
+        return np.frombuffer(raw, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+
+    def tensor(self, t: np.ndarray) -> Buf:
+        """A buffer holding ``t`` as the kernels read it (src/gpu.rs:257-262)."""
+        t = np.ascontiguousarray(t)
+        b = self.alloc(max(t.nbytes, 1))
+        if t.nbytes:
+            self.write(b, 0, t)
+        return b
+
+    def fetch(self, b: Buf, dtype, shape) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        return self.read(b, 0, out)
+
+    # -- kernels ---------------------------------------------------------------
+    def kernel(self, name: str, shapes: Sequence[Sequence[int]]) -> K:
+        """Kernel ``name`` for these array shapes, made once and then reused.
+
+        The reference's ``file``, ``meta`` and ``warps`` arguments
+        (src/gpu.rs:148-155) have no equivalent: tile shapes are chosen in the
+        library.
+        """
+        flat = [int(d) for s in shapes for d in s]
+        ranks = [len(s) for s in shapes]
+        fa = (C.c_int64 * max(len(flat), 1))(*flat)
+        ra = (C.c_int32 * max(len(ranks), 1))(*ranks)
+        out = C.c_int32()
+        self._check(self._l.tb200_kernel(self._h, name.encode(), fa, ra, len(ranks), C.byref(out)))
+        last = list(shapes[-1]) if shapes else []
+        self._names[out.value] = f"{name} -> {last}"
+        return K(out.value, name)
+
+    def launch(self, k: K, args: Sequence[Arg]) -> None:
+        """Launches ``k`` (asynchronously)."""
+        raw = (C.c_uint64 * max(len(args), 1))(*[_bits(a) for a in args])
+        self.launches += 1
+        if self.profile is None:
+            self._check(self._l.tb200_launch(self._h, k.id, raw, len(args)))
+            return
+        self._check(self._l.tb200_time_begin(self._h))
+        self._check(self._l.tb200_launch(self._h, k.id, raw, len(args)))
+        ms = C.c_float()
+        self._check(self._l.tb200_time_end(self._h, C.byref(ms)))
+        e = self.profile.setdefault((self.phase, self._names[k.id]), [0, 0.0])
+        e[0] += 1
+        e[1] += ms.value
+
+    def profile_rows(self):
+        """The profile, largest first: (phase, kernel, launches, milliseconds)."""
+        rows = [(p, k, int(n), ms) for (p, k), (n, ms) in (self.profile or {}).items()]
+        rows.sort(key=lambda r: -r[3])
+        return rows
+
+    # -- graphs, sync, timing ----------------------------------------------------
+    def capture_begin(self) -> None:
+        self._check(self._l.tb200_capture_begin(self._h))
+
+    def capture_end(self) -> int:
+        g = C.c_int32()
+        self._check(self._l.tb200_capture_end(self._h, C.byref(g)))
+        return g.value
+
+    def replay(self, g: int) -> None:
+        self.launches += 1
+        self._check(self._l.tb200_replay(self._h, g))
+
+    def sync(self) -> None:
+        self._check(self._l.tb200_sync(self._h))
+
+    def time_begin(self) -> None:
+        self._check(self._l.tb200_time_begin(self._h))
+
+    def time_end(self) -> float:
+        ms = C.c_float()
+        self._check(self._l.tb200_time_end(self._h, C.byref(ms)))
+        return ms.value
+
+    def kernel_launches(self) -> int:
+        """Kernels launched by the library on this context."""
+        n = C.c_uint64()
+        self._check(self._l.tb200_launch_count(self._h, C.byref(n)))
+        return n.value
+
+    def set_stream(self, stream_ptr: Optional[int]) -> None:
+        self._check(self._l.tb200_set_stream(self._h, C.c_void_p(stream_ptr) if stream_ptr else None))
+
+    # -- tensor parallelism ------------------------------------------------------
+    def comm_id(self) -> bytes:
+        buf = C.create_string_buffer(_lib.COMM_ID_BYTES)
+        self._check(self._l.tb200_comm_id(self._h, buf))
+        return buf.raw
+
+    def comm_init(self, rank: int, nranks: int, comm_id: bytes) -> None:
+        buf = C.create_string_buffer(comm_id, _lib.COMM_ID_BYTES)
+        self._check(self._l.tb200_comm_init(self._h, rank, nranks, buf))
+
+    def allreduce(self, b: Buf, count: int, dtype: int = 0) -> None:
+        self._check(self._l.tb200_allreduce(self._h, b.ptr, count, dtype))
