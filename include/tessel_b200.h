@@ -74,8 +74,13 @@ int tb200_host_free(tb200_ctx* ctx, void* ptr);
  * matmul (kernels/matmul.tl:3-17), flash_attention, paged_attention
  * (kernels/attention.tl:4-51); and, with no counterpart in the reference,
  * linear_f32 (X[M,K], W[N,K], Y f32[M,N]), residual_add (R f32[M,N], P
- * f32[M,N]) and argmax_rows (X f32[M,N], out i32[M]). The reference's `meta`
- * and `warps` arguments have no equivalent: tile shapes are chosen inside. */
+ * f32[M,N]), argmax_rows (X f32[M,N], out i32[M]) and decode_advance
+ * (picked[T], tok[T], pos[T], slot[T], lens[T], table[T,MP], hist[S,T], then
+ * the i32 scalars n, P and step: the next decode step's inputs for rows < n,
+ * computed on the device as src/llm/sched.rs:139-144 computes them on the
+ * host, the picks also stored in hist[step]). The
+ * reference's `meta` and `warps` arguments have no equivalent: tile shapes are
+ * chosen inside. */
 int tb200_kernel(tb200_ctx* ctx, const char* name, const int64_t* shapes, const int32_t* ranks, int n_arrays,
                  tb200_op* out);
 

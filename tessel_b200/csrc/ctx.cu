@@ -80,6 +80,7 @@ static const KindInfo KINDS[] = {
     {"linear_f32", K_LINEAR_F32, 3, 3},
     {"residual_add", K_RESIDUAL_ADD, 2, 2},
     {"argmax_rows", K_ARGMAX_ROWS, 2, 2},
+    {"decode_advance", K_DECODE_ADVANCE, 7, 10},
 };
 
 static bool is_gemm(Kind k) {

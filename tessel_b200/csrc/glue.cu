@@ -268,6 +268,24 @@ __global__ void argmax_rows_kernel(const float* __restrict__ X, int* __restrict_
   }
 }
 
+// After a greedy decode step: row b < n takes its pick as the next token, moves one position
+// on, and gets the cache slot of that position from its block table (page * P + offset, as
+// src/llm/sched.rs:139-144 computes them on the host). Rows >= n stay padding. The picks are
+// also appended to row `step` of the history hist[S, T].
+__global__ void decode_advance_kernel(const int* __restrict__ picked, int* __restrict__ tok, int* __restrict__ pos,
+                                      int* __restrict__ slot, int* __restrict__ lens, const int* __restrict__ table,
+                                      int* __restrict__ hist, int MP, int n, int P) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n) return;
+  const int p = pos[b] + 1;
+  tok[b] = picked[b];
+  hist[b] = picked[b];
+  pos[b] = p;
+  lens[b] = p + 1;
+  const int col = p / P;
+  slot[b] = col < MP ? table[(size_t)b * MP + col] * P + p % P : 0x7fffffff;  // past the table: dropped write
+}
+
 int grid_for(long long items, int block, int sms) {
   long long g = (items + block - 1) / block;
   const long long cap = (long long)sms * 16;
@@ -315,6 +333,10 @@ int make_glue(Ctx* c, Op& op) {
       break;
     case K_ARGMAX_ROWS:
       if (s[0].size() != 2 || s[1][0] != s[0][0] || s[0][1] < 1) return bad("shapes are X[M,N], out[M]");
+      break;
+    case K_DECODE_ADVANCE:
+      if (s[5].size() != 2 || s[5][0] != s[0][0] || s[6].size() != 2 || s[6][1] != s[0][0])
+        return bad("shapes are picked[T], tok[T], pos[T], slot[T], lens[T], table[T,MP], hist[S,T]");
       break;
     default:
       return bad("not a glue kernel");
@@ -387,6 +409,17 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
       const int M = (int)s[0][0], N = (int)s[0][1];
       if (M == 0) return 0;
       argmax_rows_kernel<<<M, 1024, 0, st>>>((const float*)a[0], (int*)a[1], N);
+      break;
+    }
+    case K_DECODE_ADVANCE: {
+      const int T = (int)s[0][0], MP = (int)s[5][1];
+      const int n = (int)(uint32_t)a[7], P = (int)(uint32_t)a[8], step = (int)(uint32_t)a[9];
+      if (n < 0 || n > T || P < 1) return fail(c, "decode_advance: 0 <= n <= T and P >= 1");
+      if (step < 0 || step >= (int)s[6][0]) return fail(c, "decode_advance: step outside the history");
+      if (n == 0) return 0;
+      decode_advance_kernel<<<(n + 127) / 128, 128, 0, st>>>((const int*)a[0], (int*)a[1], (int*)a[2], (int*)a[3],
+                                                             (int*)a[4], (const int*)a[5], (int*)a[6] + (size_t)step * T,
+                                                             MP, n, P);
       break;
     }
     default:

@@ -155,6 +155,8 @@ class Engine:
         self._stage = gpu.host_array((6 * t + t * mp,), np.int32)
         self._picked_host = gpu.host_array((t,), np.int32)
         self._logits_host: Optional[np.ndarray] = None
+        self._hist: Optional[Buf] = None
+        self._hist_rows = 0
 
     # -- one step ----------------------------------------------------------------
     def _upload(self, tokens, pos, slots, attn, want):
@@ -255,6 +257,36 @@ class Engine:
             return np.empty((0,), np.int32)
         out = self._picked_host[:len(want)]
         self.gpu.read(self.picked, 0, out)
+        return out
+
+    def decode_resident(self, n: int, steps: int) -> np.ndarray:
+        """``steps`` more greedy decode steps for the ``n`` sequences of the decode step that just
+        ran (``step_greedy`` with ``Decode``), with no host input in between: after each step a
+        small kernel turns the picks into the next step's token, position, cache slot and length
+        on the device, and the recorded step is replayed. Returns int32 ``[steps, n]``: the token
+        picked by each of these steps. The sequences' block tables must already hold the pages
+        their new tokens land in (the scheduler reserves them up front)."""
+        from .gpu import I32
+        t = padded(n)
+        if steps < 1:
+            return np.empty((0, n), np.int32)
+        if self._hist is None or self._hist_rows < steps:
+            self._hist = self.gpu.alloc(steps * self.tmax * 4)
+            self._hist_rows = steps
+        g = self.gpu
+        adv = g.kernel("decode_advance", [[t], [t], [t], [t], [t], [t, self.lim.max_seq_pages], [self._hist_rows, t]])
+        for s in range(steps):
+            g.launch(adv, [self.picked, self.tok, self.pos, self.slot, self.lens, self.table, self._hist, I32(n),
+                           I32(self.lim.page), I32(s)])
+            self._run(t, False, t, True)
+        # Row s of the history holds the picks that FED step s; the last step's own picks are in `picked`.
+        out = np.empty((steps, n), np.int32)
+        if steps > 1:
+            h = np.empty((steps, t), np.int32)
+            g.read(self._hist, 0, h)
+            out[:-1] = h[1:, :n]
+        g.read(self.picked, 0, self._picked_host[:n])
+        out[-1] = self._picked_host[:n]
         return out
 
     # -- the launch sequence -------------------------------------------------------

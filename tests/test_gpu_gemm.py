@@ -1,0 +1,102 @@
+"""The tcgen05 projections against the CPU oracle, through the C ABI: every epilogue, the
+decode and prompt row counts the engine uses, ragged sizes (rows and columns that are not
+tile multiples, K that is not a multiple of 64), the reference's tuning-test shapes
+(tests/llm.rs:107-187) and its (100, 70, 90) matmul whose pitch TMA cannot address; and at
+4096^3 sampled entries in f64 (src/bench.rs:86-98) plus linearity."""
+import numpy as np
+import pytest
+
+import oracle
+from refs import matmul_ref, rel_err
+from tessel_b200.gpu import F32
+
+pytestmark = pytest.mark.gpu
+h, f, i32 = np.float16, np.float32, np.int32
+TOL = 2e-3
+
+
+def launch(gpu, name, arrays, out):
+    bufs = [gpu.tensor(a) for a in arrays]
+    k = gpu.kernel(name, [a.shape for a in arrays])
+    gpu.launch(k, bufs)
+    gpu.sync()
+    y = gpu.fetch(bufs[out], arrays[out].dtype, arrays[out].shape)
+    for b in bufs:
+        gpu.free(b)
+    return y
+
+
+SHAPES = [(16, 96, 256), (32, 96, 256), (64, 96, 256),       # tests/llm.rs:118-119
+          (16, 512, 128), (256, 6144, 4096), (256, 4096, 512), (100, 200, 72),
+          (128, 256, 64), (129, 264, 200), (300, 40, 1032), (2048, 512, 256), (1, 8, 8)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_linear_family(gpu, M, N, K):
+    r = oracle.Rng(31)
+    x, w = r.tensor(h, (M, K)), r.tensor(h, (N, K), 0.1)
+    res = r.tensor(f, (M, N))
+    big = M * N * K > 1 << 28
+    rows = np.unique(np.linspace(0, M - 1, 16).astype(int)) if big else np.arange(M)
+    y = launch(gpu, "linear", [x, w, np.zeros((M, N), h)], 2)
+    assert rel_err(y[rows], oracle.linear(x[rows], w)) <= TOL
+    y = launch(gpu, "logits", [x, w, np.full((M, N), 3, f)], 2)
+    assert rel_err(y[rows], oracle.logits(x[rows], w)) <= TOL
+    y = launch(gpu, "linear_f32", [x, w, np.full((M, N), 3, f)], 2)
+    assert rel_err(y[rows], oracle.logits(x[rows], w)) <= TOL
+    y = launch(gpu, "linear_residual", [x, w, res.copy()], 2)
+    assert rel_err(y[rows], oracle.linear_residual(x[rows], w, res[rows])) <= TOL
+
+
+@pytest.mark.parametrize("M,F,K", [(16, 96, 256), (64, 96, 256), (16, 256, 128), (256, 14336 // 8, 4096),
+                                   (130, 200, 136), (2048, 256, 128)])
+def test_gate_up(gpu, M, F, K):
+    r = oracle.Rng(32)
+    x, wg, wu = r.tensor(h, (M, K)), r.tensor(h, (F, K), 0.1), r.tensor(h, (F, K), 0.1)
+    y = launch(gpu, "gate_up", [x, wg, wu, np.zeros((M, F), h)], 3)
+    rows = np.unique(np.linspace(0, M - 1, 24).astype(int))
+    assert rel_err(y[rows], oracle.gate_up(x[rows], wg, wu)) <= TOL
+
+
+@pytest.mark.parametrize("M,K,N", [(100, 70, 90), (128, 64, 64), (256, 128, 256), (200, 136, 328), (512, 1024, 2048)])
+def test_matmul_row_major_b(gpu, M, K, N):
+    """kernels/matmul.tl:3-17: B is [K, N] row-major (an N-major operand for the tensor core)."""
+    r = oracle.Rng(3)
+    a, b = r.tensor(h, (M, K)), r.tensor(h, (K, N))
+    c = launch(gpu, "matmul", [a, b, np.zeros((M, N), h)], 2)
+    assert rel_err(c, matmul_ref(a, b, False)) <= TOL
+    if M * N * K <= 1 << 24:
+        assert rel_err(c, oracle.matmul(a, b)) <= TOL
+
+
+def test_matmul_4096_cubed(gpu):
+    """BASELINE config 2: A, B ~U[-1,1] seeded, f16, f32 accumulation, f16 out; 256 sampled
+    entries in f64, whole rows against the oracle, and C(A, B1 + B2) = C(A, B1) + C(A, B2)
+    for operands chosen so that the sums are exact."""
+    n = 4096
+    r = oracle.Rng(1)
+    a, b = r.tensor(h, (n, n)), r.tensor(h, (n, n))
+    c = launch(gpu, "matmul", [a, b, np.zeros((n, n), h)], 2)
+    g = np.random.default_rng(0)
+    ii, jj = g.integers(0, n, 256), g.integers(0, n, 256)
+    want = np.einsum("sk,ks->s", a[ii].astype(np.float64), b[:, jj].astype(np.float64))
+    assert np.abs(c[ii, jj].astype(np.float64) - want).max() / np.abs(want).max() <= TOL
+    rows = [0, 1, 2047, 4095]
+    want_rows = np.concatenate([oracle.matmul_block(a, b, i, i + 1, 0, n) for i in rows])
+    assert rel_err(c[rows], want_rows) <= TOL
+    # Linearity with small-integer operands: every product and sum is exact in f32 and f16.
+    ai = g.integers(-2, 3, (256, 256)).astype(h)
+    b1, b2 = g.integers(-2, 3, (256, 256)).astype(h), g.integers(-2, 3, (256, 256)).astype(h)
+    c1 = launch(gpu, "matmul", [ai, b1, np.zeros((256, 256), h)], 2).astype(f)
+    c2 = launch(gpu, "matmul", [ai, b2, np.zeros((256, 256), h)], 2).astype(f)
+    c12 = launch(gpu, "matmul", [ai, (b1 + b2).astype(h), np.zeros((256, 256), h)], 2).astype(f)
+    assert np.array_equal(c12, c1 + c2)
+    assert np.array_equal(c1, (ai.astype(f) @ b1.astype(f)))
+
+
+def test_empty_shapes(gpu):
+    x = np.zeros((0, 64), h)
+    w = np.ones((32, 64), h)
+    assert launch(gpu, "linear", [x, w, np.zeros((0, 32), h)], 2).shape == (0, 32)
+    y = launch(gpu, "linear", [np.zeros((4, 0), h), np.zeros((8, 0), h), np.ones((4, 8), h)], 2)
+    assert not y.any()

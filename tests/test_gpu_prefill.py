@@ -1,0 +1,92 @@
+"""Causal FlashAttention (packed GQA prefill and the plain [H,S,D] layout) against the CPU
+oracle and the f64 procedure of the reference's tests."""
+import numpy as np
+import pytest
+
+import oracle
+from refs import attention_ref, rel_err
+from tessel_b200.gpu import F32
+
+pytestmark = pytest.mark.gpu
+h, f, i32 = np.float16, np.float32, np.int32
+TOL = 2e-3
+
+
+def prefill(gpu, q, k, v, starts, scale):
+    arrays = [q, k, v, starts, np.zeros(q.shape, h)]
+    bufs = [gpu.tensor(a) for a in arrays]
+    kern = gpu.kernel("prefill_attention", [a.shape for a in arrays])
+    gpu.launch(kern, bufs + [F32(scale)])
+    gpu.sync()
+    o = gpu.fetch(bufs[4], h, q.shape)
+    for b in bufs:
+        gpu.free(b)
+    return o
+
+
+def flash(gpu, q, k, v, scale):
+    arrays = [q, k, v, np.zeros(q.shape, h)]
+    bufs = [gpu.tensor(a) for a in arrays]
+    kern = gpu.kernel("flash_attention", [a.shape for a in arrays])
+    gpu.launch(kern, bufs + [F32(scale)])
+    gpu.sync()
+    o = gpu.fetch(bufs[3], h, q.shape)
+    for b in bufs:
+        gpu.free(b)
+    return o
+
+
+def starts_of(lengths, total):
+    s = np.arange(total, dtype=i32)  # padding rows start at themselves
+    at = 0
+    for n in lengths:
+        s[at:at + n] = at
+        at += n
+    return s
+
+
+@pytest.mark.parametrize("H,G,D,lengths,pad", [
+    (4, 2, 64, [70, 26], 0),                 # examples/metal_cases.rs:176-177
+    (4, 2, 64, [10], 6),                     # one prompt, padded to 16 rows
+    (8, 2, 128, [300, 5, 129, 64], 14),      # blocks that straddle prompts; a start after a whole key block
+    (32, 8, 128, [257], 255),
+    (4, 2, 16, [70, 20], 38),                # the tiny test model (generic path)
+    (2, 2, 32, [150], 0),
+])
+def test_packed_prefill(gpu, H, G, D, lengths, pad):
+    S = sum(lengths) + pad
+    r = oracle.Rng(41)
+    q, k, v = r.tensor(h, (S, H, D)), r.tensor(h, (S, G, D)), r.tensor(h, (S, G, D))
+    st = starts_of(lengths, S)
+    scale = float(1.0 / np.sqrt(D))
+    got = prefill(gpu, q, k, v, st, scale)
+    want = oracle.prefill_attention(q, k, v, st, scale)
+    assert not np.isnan(got.astype(f)).any()
+    assert rel_err(got, want) <= TOL
+
+
+@pytest.mark.parametrize("H,S,D", [(2, 150, 32), (3, 200, 64), (2, 384, 128), (1, 1, 128)])
+def test_flash_attention(gpu, H, S, D):
+    """tests/interp.rs:103-124 at (2, 150, 32), and tile-multiple / ragged lengths on the tensor-core path."""
+    r = oracle.Rng(4)
+    q, k, v = (r.tensor(h, (H, S, D)) for _ in range(3))
+    scale = float(1.0 / np.sqrt(D))
+    got = flash(gpu, q, k, v, scale)
+    assert rel_err(got, oracle.flash_attention(q, k, v, scale)) <= TOL
+    assert rel_err(got, attention_ref(q, k, v, scale)) <= 5e-3
+
+
+def test_config3_shape_sampled(gpu):
+    """BASELINE config 3 (batch 8 x 32 heads folded into H = 256, S 4096, D 128, ~N(0,1)): a
+    few (head, row-block) programs against the oracle; and the first row of every head
+    attends to itself only, so O[h, 0] == V[h, 0] exactly."""
+    g = np.random.default_rng(3)
+    H, S, D = 256, 4096, 128
+    q, k, v = (g.standard_normal((H, S, D), dtype=f).astype(h) for _ in range(3))
+    scale = float(1.0 / np.sqrt(D))
+    got = flash(gpu, q, k, v, scale)
+    assert np.array_equal(got[:, 0].view(np.uint16), v[:, 0].view(np.uint16))
+    for hh, blk in [(0, 0), (17, 31), (255, 63), (100, 7)]:
+        want = oracle.flash_attention(q[hh:hh + 1], k[hh:hh + 1], v[hh:hh + 1], scale, blocks=(blk, blk + 1))
+        rows = slice(blk * 64, blk * 64 + 64)
+        assert rel_err(got[hh, rows], want[0, rows]) <= TOL
