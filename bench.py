@@ -1,0 +1,419 @@
+"""Decode throughput of the Llama-3-8B-shaped engine (BASELINE config 5) on N B200s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A "step" is one decode step of the whole batch: 256 sequences (prompts of 512-2048 uniform
+random token ids, random-init f16 weights ~N(0, 0.02)), one new token each, greedy. The
+prompts are prefilled through the engine first (untimed), then W warm-up decode steps, then
+
+  * `e2e`:   K decode steps through `Engine.step_greedy` with HOST inputs: each step uploads
+             the step's tokens, positions, slots, block tables and lengths from page-locked
+             memory and reads the picked tokens back;
+  * `value`: K decode steps with everything resident on the device (`Engine.decode_resident`:
+             a small kernel derives the next step's inputs from the picks, the recorded step
+             is replayed).
+
+Both are timed with CUDA events on the stream the kernels run on, between synchronisations,
+and the maximum over ranks is taken. With N > 1 the model is tensor-parallel over the N GPUs
+(attention/KV heads and MLP columns sharded, one NCCL allreduce after o_proj and after
+down_proj), so the job is the same 256 sequences: strong scaling.
+
+`--impl reference` times the CPU restatement of the reference's interpreter path (the
+oracle; the reference itself is Rust and cannot be built on these machines) on the host
+cores, on a bounded sample of the same decode step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tok/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama3-8b", choices=["llama3-8b", "tinyllama"])
+    ap.add_argument("--seqs", type=int, default=0, help="sequences (default: the workload's)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile-steps", type=int, default=2)
+    return ap.parse_args()
+
+
+def workload(name: str):
+    from tessel_b200.model import Config
+    if name == "llama3-8b":
+        return dict(cfg=Config.llama3_8b(max_pos=2304), seqs=256, lo=512, hi=2048, new=256,
+                    label="Llama-3-8B shape, 256 seqs, prompts U[512,2048], 256 new tokens, page 16")
+    return dict(cfg=Config.tinyllama(max_pos=1152), seqs=64, lo=128, hi=1024, new=128,
+                label="TinyLlama-1.1B shape, 64 seqs, prompts U[128,1024], 128 new tokens, page 16")
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return dict(hbm=float(j["hbm_gbs"]), tflops=float(j["bf16_tflops"]), kind="measured")
+    return dict(hbm=6650.0, tflops=1590.0, kind="fallback")
+
+
+class Clocks:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                       "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.f,
+                                      stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.p.terminate()
+        self.p.wait()
+        self.f.flush()
+        rows = [l.strip().split(", ") for l in open(self.f.name) if l.strip()]
+        os.unlink(self.f.name)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[4:8]):
+                if v.strip().lower() == "active":
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---- the CPU arm: the oracle on the host cores -----------------------------------------------
+def cpu_decode_sample(cfg, ctx, rows: int, head_div: int = 8):
+    """Times one layer and 1/head_div of the LM head of a decode step for `rows` sequences on
+    the oracle, and scales to the whole step (all layers, whole head, all sequences).
+    Returns (seconds for the sample, extrapolated seconds per full step)."""
+    import oracle
+    g = np.random.default_rng(0)
+    h = np.float16
+    dm, H, G, D, F, V = cfg.dim, cfg.heads, cfg.kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab
+    W = (H + 2 * G) * D
+    P = 16
+
+    def m(r, c):
+        return (g.standard_normal((r, c), dtype=np.float32) * np.float32(0.02)).astype(h)
+
+    wqkv, wo, wg, wu, wd = m(W, dm), m(dm, H * D), m(F, dm), m(F, dm), m(dm, F)
+    vs = V // head_div
+    head = m(vs, dm)
+    one = np.ones(dm, h)
+    lens = np.asarray(ctx[:rows], np.int32) + 1
+    pages = [-(-int(l) // P) for l in lens]
+    NP = sum(pages) + 1
+    kc = g.standard_normal((NP, P, G, D), dtype=np.float32).astype(h)
+    vc = g.standard_normal((NP, P, G, D), dtype=np.float32).astype(h)
+    MP = max(pages)
+    table = np.zeros((rows, MP), np.int32)
+    at = 0
+    for b, n in enumerate(pages):
+        table[b, :n] = np.arange(at, at + n)
+        at += n
+    x = g.standard_normal((rows, dm), dtype=np.float32)
+    pos = (lens - 1).astype(np.int32)
+    slot = np.asarray([table[b, pos[b] // P] * P + pos[b] % P for b in range(rows)], np.int32)
+    Ct, St = oracle.rope_tables(cfg.max_pos, D, cfg.rope_theta)
+    t0 = time.perf_counter()
+    hh = oracle.rmsnorm(x, one, cfg.eps)
+    qkv = oracle.linear(hh, wqkv)
+    q = oracle.rope_q(qkv, pos, Ct, St, H, D)
+    kc2, vc2, _, _ = oracle.kv_write(qkv, pos, slot, Ct, St, kc.reshape(NP * P, G, D), vc.reshape(NP * P, G, D), G, D)
+    o = oracle.decode_attention(q, kc2.reshape(NP, P, G, D), vc2.reshape(NP, P, G, D), table, lens,
+                                1.0 / math.sqrt(D))
+    x = oracle.linear_residual(o.reshape(rows, H * D), wo, x)
+    hh = oracle.rmsnorm(x, one, cfg.eps)
+    mlp = oracle.gate_up(hh, wg, wu)
+    x = oracle.linear_residual(mlp, wd, x)
+    t_layer = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    last = oracle.rmsnorm_rows(x, np.arange(rows, dtype=np.int32), one, cfg.eps)
+    lg = oracle.logits(last, head)
+    [oracle.argmax(r) for r in lg]
+    t_head = time.perf_counter() - t0
+    return t_layer + t_head, (t_layer * cfg.layers + t_head * head_div) * (len(ctx) / rows)
+
+
+def run_reference(args, wl):
+    """The reference arm: rank 0 times the oracle; other ranks leave."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import oracle
+    cfg = wl["cfg"]
+    seqs = args.seqs or wl["seqs"]
+    g = np.random.default_rng(1)
+    ctx = g.integers(wl["lo"], wl["hi"] + 1, seqs)
+    rows = 16
+    # Size the sample so that K + W steps end within a few minutes.
+    t, _ = cpu_decode_sample(cfg, ctx, rows)
+    while rows > 1 and t * (args.steps + args.warmup) > 150.0:
+        rows //= 2
+        t, _ = cpu_decode_sample(cfg, ctx, rows)
+    for _ in range(max(0, args.warmup - 1)):
+        cpu_decode_sample(cfg, ctx, rows)
+    full = []
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        full.append(cpu_decode_sample(cfg, ctx, rows)[1])
+    wall = time.perf_counter() - t0
+    sec = statistics.mean(full)
+    val = seqs / sec
+    sample = (f"per step: 1 of {cfg.layers} layers and 1/8 of the LM head for {rows} of {seqs} sequences, "
+              f"scaled to the whole decode step; {wall / args.steps:.2f} s of CPU work per step")
+    line = {"metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "impl": "reference",
+            "config": {"workload": wl["label"], "parallelism": "cpu"},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": oracle.threads(), "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ---- our arm ---------------------------------------------------------------------------------
+def device_weights(cfg, local, seed, torch):
+    """Random-init f16 weights ~N(0, 0.02) generated on the device, this rank's shard only."""
+    from tessel_b200.model import DevArray, Layer, Weights
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    keep = []
+
+    def m(r, c):
+        t = torch.empty((r, c), dtype=torch.float16, device="cuda")
+        t.normal_(0.0, 0.02, generator=gen)
+        keep.append(t)
+        return DevArray(t.data_ptr(), (r, c), np.float16, t)
+
+    def ones(n):
+        t = torch.ones((n,), dtype=torch.float16, device="cuda")
+        keep.append(t)
+        return DevArray(t.data_ptr(), (n,), np.float16, t)
+
+    layers = [Layer(ones(cfg.dim), m(local.qkv(), cfg.dim), m(cfg.dim, local.heads * cfg.head_dim), ones(cfg.dim),
+                    m(local.ffn, cfg.dim), m(local.ffn, cfg.dim), m(cfg.dim, local.ffn)) for _ in range(cfg.layers)]
+    # The embedding and the LM head must be the same on every rank: a generator of their own.
+    gen.manual_seed(12345)
+    return Weights(local, m(cfg.vocab, cfg.dim), layers, ones(cfg.dim), m(cfg.vocab, cfg.dim))
+
+
+def run_ours(args, wl):
+    import torch
+    import torch.distributed as dist
+    from tessel_b200.engine import Engine, Limits, padded
+    from tessel_b200.gpu import Gpu
+    from tessel_b200.model import Config
+    from tessel_b200.sched import Request, Scheduler
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {world}: launch with torch.distributed.run")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: there is no CPU path (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    cfg = wl["cfg"]
+    seqs = args.seqs or wl["seqs"]
+    K, Wm = args.steps, args.warmup
+    # Decode steps this run needs from every sequence: warm-up, two timed regions, profiling.
+    need_new = max(wl["new"], Wm + 2 * K + args.profile_steps + 4)
+    P = 16
+    max_prompt = wl["hi"]
+    cfg.max_pos = max(cfg.max_pos, max_prompt + need_new)
+    msp = -(-(max_prompt + need_new) // P)
+    if cfg.heads % world or cfg.kv_heads % world or cfg.ffn % world:
+        raise SystemExit(f"{world} ranks do not divide heads/kv_heads/ffn")
+    local = Config(**{**cfg.__dict__, "heads": cfg.heads // world, "kv_heads": cfg.kv_heads // world,
+                      "ffn": cfg.ffn // world})
+    g = np.random.default_rng(1)
+    plens = g.integers(wl["lo"], wl["hi"] + 1, seqs)
+    reqs = [Request(g.integers(0, cfg.vocab, int(n)).tolist(), need_new) for n in plens]
+    pages = int(sum(-(-(int(n) + need_new) // P) for n in plens)) + 8
+
+    gpu = Gpu(local_rank)
+    if world > 1:
+        ids = [gpu.comm_id() if rank == 0 else None]
+        dist.broadcast_object_list(ids, src=0)
+        gpu.comm_init(rank, world, ids[0])
+    w = device_weights(cfg, local, 1000 + rank, torch)
+    e = Engine(gpu, w, Limits(page=P, pages=pages, max_tokens=max_prompt, max_seq_pages=msp), rank=rank,
+               nranks=world, sharded=True)
+    s = Scheduler(e, reqs, seqs, packed=True, device_argmax=True)
+
+    # ---- prefill (untimed for the metric; reported for information) ---------------------------
+    t0 = time.perf_counter()
+    while s.waiting:
+        if s.step() != "prefill":
+            raise SystemExit("the cache cannot hold the whole batch")
+    gpu.sync()
+    prefill_s = time.perf_counter() - t0
+    n = len(s.running)
+    t = padded(n)
+
+    for _ in range(max(Wm, 3)):
+        s.step()
+    gpu.sync()
+
+    clocks = Clocks(local_rank)
+    # ---- e2e: host inputs every step ------------------------------------------------------------
+    launches0 = gpu.kernel_launches()
+    barrier()
+    gpu.sync()
+    clocks.start()
+    gpu.time_begin()
+    for _ in range(K):
+        s.step()
+    e2e_ms = gpu.time_end()
+    gpu.sync()
+    barrier()
+    e2e_ms = max_over_ranks(e2e_ms)
+    e2e_launches = gpu.kernel_launches() - launches0
+
+    # ---- value: device-resident steps ---------------------------------------------------------
+    ctx0 = [q.len for q in s.running]
+    toks, pos, slots, attn, want = s.decode_inputs()
+    s.absorb(e.step_greedy(toks, pos, slots, attn, want))  # uploads the tables the resident loop walks
+    for _ in range(2):
+        s.absorb(e.decode_resident(n, 1)[0])
+    launches0 = gpu.kernel_launches()
+    barrier()
+    gpu.sync()
+    gpu.time_begin()
+    picks = e.decode_resident(n, K)
+    dev_ms = gpu.time_end()
+    gpu.sync()
+    barrier()
+    clock_rec = clocks.stop()
+    dev_ms = max_over_ranks(dev_ms)
+    dev_launches = gpu.kernel_launches() - launches0
+    ctx_mid = float(np.mean([q.len for q in s.running])) + K / 2.0
+    for row in picks:
+        s.absorb(row)
+
+    # ---- per-kernel times: the same step, every launch timed on its own (graphs off) ------------
+    gpu.profile = {}
+    ctx_prof = [q.len + 1 for q in s.running]
+    for _ in range(args.profile_steps):
+        s.step()
+    prof = gpu.profile_rows()
+    gpu.profile = None
+    total_prof = sum(r[3] for r in prof) or 1.0
+    att = [r for r in prof if r[1].startswith("decode_attention")]
+    pk = peaks()
+    lyr = cfg.layers
+    Gl, D, Hl = local.kv_heads, cfg.head_dim, local.heads
+    sum_ctx = float(sum(ctx_prof)) + (args.profile_steps - 1) * n / 2.0
+    att_bytes = 4.0 * Gl * D * sum_ctx + 4.0 * n * Hl * D + 4.0 * sum(-(-c // P) for c in ctx_prof) + 4.0 * n
+    roof = None
+    if att:
+        att_ms = att[0][3] / att[0][2]
+        achieved = att_bytes / (att_ms * 1e-3) / 1e9
+        roof = {"kernel": "decode_attention", "bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
+                "frac": achieved / pk["hbm"], "peak_kind": pk["kind"], "traffic": None,
+                "algorithmic_bytes_per_launch": att_bytes, "ms_per_launch": att_ms,
+                "share_of_step": att[0][3] / total_prof}
+    # Whole-step HBM roofline (weights once, KV once per KV head), per GPU.
+    wbytes = 2.0 * (lyr * (local.qkv() * cfg.dim + cfg.dim * Hl * D + 3 * local.ffn * cfg.dim) + cfg.vocab * cfg.dim)
+    kvbytes = 4.0 * Gl * D * lyr * ctx_mid * n
+    step_bytes = wbytes + kvbytes
+    dev_step_ms = dev_ms / K
+    step_roof = {"bytes_per_step_per_gpu": step_bytes, "weights_bytes": wbytes, "kv_bytes": kvbytes,
+                 "achieved_gbs": step_bytes / (dev_step_ms * 1e-3) / 1e9, "peak_gbs": pk["hbm"],
+                 "frac": step_bytes / (dev_step_ms * 1e-3) / 1e9 / pk["hbm"], "mean_context": ctx_mid}
+
+    if rank != 0:
+        barrier()
+        return
+    value = n * K / (dev_ms * 1e-3)
+    mp = msp
+    h2d = 4 * (3 * t + t + t + t * mp)  # tok, pos, slot, idx, lens, table
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(Wm, 3),
+        "ms_per_step": dev_step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": wl["label"], "sequences": n, "parallelism": f"tp{world}",
+                   "l2": "inputs larger than L2 (weights + KV read per step: %.1f GB per GPU)" % (step_bytes / 1e9),
+                   "mean_context": ctx_mid},
+        "e2e": {"value": n * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * n,
+                "ms_per_step": e2e_ms / K},
+        "gpu_launches": int(dev_launches), "e2e_gpu_launches": int(e2e_launches),
+        "clocks": clock_rec,
+        "roofline": roof, "step_roofline": step_roof,
+        "kernel_shares": [{"kernel": r[1], "launches": r[2], "ms": round(r[3], 3), "share": round(r[3] / total_prof, 4)}
+                          for r in prof[:12]],
+        "prefill": {"seconds": prefill_s, "prompt_tokens": int(s.st.prompt_tokens),
+                    "tok_s": s.st.prompt_tokens / prefill_s, "steps": s.st.prefill_steps},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        import oracle
+        sample_s, full_s = cpu_decode_sample(cfg, [q.len for q in s.running], 16)
+        line["cpu_baseline"] = {
+            "value": n / full_s, "unit": UNIT, "cores": oracle.threads(), "kind": "port",
+            "sample": (f"1 of {cfg.layers} layers and 1/8 of the LM head for 16 of {n} sequences at their current "
+                       f"contexts, scaled to the whole decode step; {sample_s:.1f} s of CPU work")}
+    print(json.dumps(line), flush=True)
+    barrier()
+
+
+def main():
+    args = parse()
+    wl = workload(args.workload)
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    main()

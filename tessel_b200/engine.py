@@ -105,11 +105,13 @@ class _DevLayer:
 class Engine:
     """``w`` holds the full model; with ``nranks > 1`` this engine keeps rank ``rank``'s shard of it."""
 
-    def __init__(self, gpu: Gpu, w: Weights, lim: Limits, rank: int = 0, nranks: int = 1):
+    def __init__(self, gpu: Gpu, w: Weights, lim: Limits, rank: int = 0, nranks: int = 1, sharded: bool = False):
+        """``sharded``: ``w`` already is this rank's shard (its ``cfg`` the local shape)."""
         full = w.cfg
         if full.heads % full.kv_heads or full.head_dim % 2:
             raise ValueError("heads must be a multiple of kv_heads, head_dim even")
-        w = shard_weights(w, rank, nranks)
+        if not sharded:
+            w = shard_weights(w, rank, nranks)
         cfg = w.cfg
         self.gpu = gpu
         self.cfg = cfg
@@ -271,8 +273,8 @@ class Engine:
         if steps < 1:
             return np.empty((0, n), np.int32)
         if self._hist is None or self._hist_rows < steps:
-            self._hist = self.gpu.alloc(steps * self.tmax * 4)
-            self._hist_rows = steps
+            self._hist_rows = max(steps, 512)
+            self._hist = self.gpu.alloc(self._hist_rows * self.tmax * 4)
         g = self.gpu
         adv = g.kernel("decode_advance", [[t], [t], [t], [t], [t], [t, self.lim.max_seq_pages], [self._hist_rows, t]])
         for s in range(steps):

@@ -142,7 +142,10 @@ class Gpu:
         return np.frombuffer(raw, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
 
     def tensor(self, t: np.ndarray) -> Buf:
-        """A buffer holding ``t`` as the kernels read it (src/gpu.rs:257-262)."""
+        """A buffer holding ``t`` as the kernels read it (src/gpu.rs:257-262). A tensor that is
+        already on the device (``model.DevArray``) is used where it lies."""
+        if hasattr(t, "ptr") and hasattr(t, "nbytes") and not isinstance(t, np.ndarray):
+            return Buf(int(t.ptr), int(t.nbytes))
         t = np.ascontiguousarray(t)
         b = self.alloc(max(t.nbytes, 1))
         if t.nbytes:

@@ -52,6 +52,20 @@ class Config:
 
 
 @dataclass
+class DevArray:
+    """A tensor that already lives in device memory (allocated by another library of this
+    process, which ``keep`` keeps alive): accepted wherever weights take a numpy array."""
+    ptr: int
+    shape: tuple
+    dtype: object
+    keep: object = None
+
+    @property
+    def nbytes(self) -> int:
+        return int(np.prod(self.shape)) * np.dtype(self.dtype).itemsize
+
+
+@dataclass
 class Layer:
     attn_norm: np.ndarray
     wqkv: np.ndarray  # [(H + 2G) * D, dim]: q, k and v projections stacked

@@ -55,6 +55,123 @@ class _Seq:
     left: int
 
 
+class Scheduler:
+    """The state of ``generate_with`` (src/llm/sched.rs:58-68) with its loop body as ``step``:
+    one call admits and prefills what fits, or decodes one token for every running sequence."""
+
+    def __init__(self, e: Engine, reqs: Sequence[Request], max_batch: int, packed: bool = True,
+                 device_argmax: bool = False):
+        self.e, self.reqs, self.packed, self.device_argmax = e, reqs, packed, device_argmax
+        self.start = time.perf_counter()
+        # Pops yield pages 0, 1, 2, ...
+        self.free: List[int] = list(range(e.lim.pages - 1, -1, -1))
+        self.waiting = deque(range(len(reqs)))
+        self.running: List[_Seq] = []
+        self.out = [Output() for _ in reqs]
+        self.st = Stats()
+        self.max_batch = min(max_batch, e.lim.max_tokens)
+
+    def done(self) -> bool:
+        return not self.waiting and not self.running
+
+    def _choose(self, attn, toks, pos, slots, want) -> List[int]:
+        if self.device_argmax:
+            return [int(t) for t in self.e.step_greedy(toks, pos, slots, attn, want)]
+        return [argmax(row) for row in self.e.step(toks, pos, slots, attn, want)]
+
+    def _admit(self) -> List[Tuple[int, List[int]]]:
+        """As many waiting prompts as the step's token budget, the batch and the free cache pages
+        allow. Pages for a whole sequence are reserved up front."""
+        e, p = self.e, self.e.lim.page
+        admit: List[Tuple[int, List[int]]] = []
+        tokens = 0
+        while self.waiting:
+            rid = self.waiting[0]
+            r = self.reqs[rid]
+            need = -(-(len(r.prompt) + r.max_new) // p)
+            if len(r.prompt) == 0 or len(r.prompt) > e.lim.max_tokens or need > e.lim.max_seq_pages:
+                raise ValueError(f"request {rid}: prompt of {len(r.prompt)} tokens does not fit")
+            room = len(self.running) + len(admit) < self.max_batch and tokens + len(r.prompt) <= e.lim.max_tokens
+            if not room or need > len(self.free) or (not self.packed and admit):
+                break
+            self.waiting.popleft()
+            tokens += len(r.prompt)
+            admit.append((rid, [self.free.pop() for _ in range(need)]))
+        return admit
+
+    def decode_inputs(self):
+        """One row per running sequence: (tokens, positions, slots, Decode(tables, lens), want)."""
+        p = self.e.lim.page
+        run = self.running
+        toks = [s.last for s in run]
+        pos = [s.len for s in run]
+        slots = [s.pages[s.len // p] * p + s.len % p for s in run]
+        return toks, pos, slots, Decode([s.pages for s in run], [s.len + 1 for s in run]), list(range(len(run)))
+
+    def absorb(self, picks: Sequence[int]) -> None:
+        """Books one decode step's picks: lengths, outputs, finished sequences and their pages."""
+        st, eos = self.st, self.e.cfg.eos
+        st.decode_steps += 1
+        st.largest_batch = max(st.largest_batch, len(self.running))
+        st.decode_tokens += len(self.running)
+        keep = []
+        for s, t in zip(self.running, picks):
+            t = int(t)
+            s.len += 1
+            s.last = t
+            s.left -= 1
+            self.out[s.id].tokens.append(t)
+            if s.left == 0 or t == eos:
+                self.out[s.id].done_s = time.perf_counter() - self.start
+                self.free.extend(s.pages)
+            else:
+                keep.append(s)
+        self.running = keep
+
+    def step(self) -> str:
+        """Runs one engine step; returns "prefill", "decode", or "idle" when nothing can run."""
+        e, p, st, reqs = self.e, self.e.lim.page, self.st, self.reqs
+        admit = self._admit()
+        if admit:
+            toks, pos, slots, starts, last = [], [], [], [], []
+            for rid, pages in admit:
+                pr = reqs[rid].prompt
+                s0, n = len(toks), len(pr)
+                toks.extend(pr)
+                pos.extend(range(n))
+                pg = np.asarray(pages, np.int64)
+                i = np.arange(n)
+                slots.extend((pg[i // p] * p + i % p).tolist())
+                starts.extend([s0] * n)
+                last.append(len(toks) - 1)
+            attn = Prefill() if len(admit) == 1 else Packed(starts)
+            picks = self._choose(attn, toks, pos, slots, last)
+            st.prefill_steps += 1
+            st.prompt_tokens += len(toks)
+            for (rid, pages), t in zip(admit, picks):
+                self.out[rid].tokens.append(t)
+                self.out[rid].first_token_s = time.perf_counter() - self.start
+                s = _Seq(rid, pages, len(reqs[rid].prompt), t, reqs[rid].max_new - 1)
+                if s.left == 0 or t == e.cfg.eos:
+                    self.out[rid].done_s = time.perf_counter() - self.start
+                    self.free.extend(s.pages)
+                else:
+                    self.running.append(s)
+            return "prefill"
+        if not self.running:
+            return "idle"
+        t0 = time.perf_counter()
+        toks, pos, slots, attn, want = self.decode_inputs()
+        self.absorb(self._choose(attn, toks, pos, slots, want))
+        st.decode_seconds += time.perf_counter() - t0
+        return "decode"
+
+    def finish(self) -> Tuple[List[Output], Stats]:
+        self.st.generated = sum(len(o.tokens) for o in self.out)
+        self.st.seconds = time.perf_counter() - self.start
+        return self.out, self.st
+
+
 def generate(e: Engine, reqs: Sequence[Request], max_batch: int) -> Tuple[List[Output], Stats]:
     """Greedy generation for every request; stops a sequence at ``max_new`` tokens or the
     model's end-of-sequence token."""
@@ -66,92 +183,8 @@ def generate_with(e: Engine, reqs: Sequence[Request], max_batch: int, packed: bo
     """``generate``, choosing whether new prompts share prefill steps (``packed``) or each takes
     its own. ``device_argmax`` picks the tokens on the GPU (``Engine.step_greedy``) instead of
     reading the logits back and choosing on the host as the reference does."""
-    start = time.perf_counter()
-    p = e.lim.page
-    free: List[int] = list(range(e.lim.pages - 1, -1, -1))
-    waiting = deque(range(len(reqs)))
-    running: List[_Seq] = []
-    out = [Output() for _ in reqs]
-    st = Stats()
-    max_batch = min(max_batch, e.lim.max_tokens)
-    eos = e.cfg.eos
-
-    def choose(attn, toks, pos, slots, want) -> List[int]:
-        if device_argmax:
-            return [int(t) for t in e.step_greedy(toks, pos, slots, attn, want)]
-        return [argmax(row) for row in e.step(toks, pos, slots, attn, want)]
-
-    while waiting or running:
-        # Admit what fits, packing the new prompts into one prefill step.
-        admit: List[Tuple[int, List[int]]] = []
-        tokens = 0
-        while waiting:
-            rid = waiting[0]
-            r = reqs[rid]
-            need = -(-(len(r.prompt) + r.max_new) // p)
-            if len(r.prompt) == 0 or len(r.prompt) > e.lim.max_tokens or need > e.lim.max_seq_pages:
-                raise ValueError(f"request {rid}: prompt of {len(r.prompt)} tokens does not fit")
-            room = len(running) + len(admit) < max_batch and tokens + len(r.prompt) <= e.lim.max_tokens
-            if not room or need > len(free) or (not packed and admit):
-                break
-            waiting.popleft()
-            tokens += len(r.prompt)
-            admit.append((rid, [free.pop() for _ in range(need)]))
-        if admit:
-            toks, pos, slots, starts, last = [], [], [], [], []
-            for rid, pages in admit:
-                pr = reqs[rid].prompt
-                s0 = len(toks)
-                n = len(pr)
-                toks.extend(pr)
-                pos.extend(range(n))
-                pg = np.asarray(pages, np.int64)
-                i = np.arange(n)
-                slots.extend((pg[i // p] * p + i % p).tolist())
-                starts.extend([s0] * n)
-                last.append(len(toks) - 1)
-            attn = Prefill() if len(admit) == 1 else Packed(starts)
-            picks = choose(attn, toks, pos, slots, last)
-            st.prefill_steps += 1
-            st.prompt_tokens += len(toks)
-            for (rid, pages), t in zip(admit, picks):
-                n = len(reqs[rid].prompt)
-                out[rid].tokens.append(t)
-                out[rid].first_token_s = time.perf_counter() - start
-                s = _Seq(rid, pages, n, t, reqs[rid].max_new - 1)
-                if s.left == 0 or t == eos:
-                    out[rid].done_s = time.perf_counter() - start
-                    free.extend(s.pages)
-                else:
-                    running.append(s)
-            continue
-        if not running:
-            continue
-        # One token for every running sequence.
-        t0 = time.perf_counter()
-        toks = [s.last for s in running]
-        pos = [s.len for s in running]
-        slots = [s.pages[s.len // p] * p + s.len % p for s in running]
-        tables = [s.pages for s in running]
-        lens = [s.len + 1 for s in running]
-        want = list(range(len(running)))
-        picks = choose(Decode(tables, lens), toks, pos, slots, want)
-        st.decode_steps += 1
-        st.largest_batch = max(st.largest_batch, len(running))
-        st.decode_tokens += len(running)
-        keep = []
-        for s, t in zip(running, picks):
-            s.len += 1
-            s.last = t
-            s.left -= 1
-            out[s.id].tokens.append(t)
-            if s.left == 0 or t == eos:
-                out[s.id].done_s = time.perf_counter() - start
-                free.extend(s.pages)
-            else:
-                keep.append(s)
-        running = keep
-        st.decode_seconds += time.perf_counter() - t0
-    st.generated = sum(len(o.tokens) for o in out)
-    st.seconds = time.perf_counter() - start
-    return out, st
+    s = Scheduler(e, reqs, max_batch, packed, device_argmax)
+    while not s.done():
+        if s.step() == "idle" and s.waiting:
+            raise ValueError(f"request {s.waiting[0]} cannot be admitted: not enough cache pages")
+    return s.finish()
