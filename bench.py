@@ -356,11 +356,14 @@ def run_ours(args, wl):
     sum_ctx = float(sum(ctx_prof)) + (args.profile_steps - 1) * n / 2.0
     att_bytes = 4.0 * Gl * D * sum_ctx + 4.0 * n * Hl * D + 4.0 * sum(-(-c // P) for c in ctx_prof) + 4.0 * n
     roof = None
+    # DRAM traffic per algorithmic byte of this kernel, from the profiler capture summarised in
+    # profiles/decode_attention_llama8b_heads_48seq.md (295.82 + 5.00 MB over 294.72 MB).
+    traffic_ratio = (295.82 + 5.00) / 294.72
     if att:
         att_ms = att[0][3] / att[0][2]
         achieved = att_bytes / (att_ms * 1e-3) / 1e9
         roof = {"kernel": "decode_attention", "bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": achieved / pk["hbm"], "peak_kind": pk["kind"], "traffic": None,
+                "frac": achieved / pk["hbm"], "peak_kind": pk["kind"], "traffic": att_bytes * traffic_ratio,
                 "algorithmic_bytes_per_launch": att_bytes, "ms_per_launch": att_ms,
                 "share_of_step": att[0][3] / total_prof}
     # Whole-step HBM roofline (weights once, KV once per KV head), per GPU.

@@ -1,0 +1,180 @@
+"""Single-kernel timings at the benchmark configurations' shapes, through the C ABI.
+
+    python -m tessel_b200.microbench decode [--seqs 256 --ctx-lo 512 --ctx-hi 2304 --heads 32 --kv-heads 8 --dim 128]
+    python -m tessel_b200.microbench gemm   [--m 4096 --n 4096 --k 4096] [--kind matmul|linear|gate_up|linear_residual]
+    python -m tessel_b200.microbench flash  [--heads 256 --seq 4096 --dim 128]
+
+Each prints one JSON line: the mean device time per launch (CUDA events on the launching
+stream, one pair per iteration, after warm-up; a 256 MB buffer is overwritten between
+iterations so that nothing is served from L2 by accident), the algorithmic bytes and flops of
+the launch (byte/flop conventions of tessel's src/bench.rs:83-84 and :132-133; KV counted once
+per KV head), and the fraction of the measured peak. Inputs are generated on the device.
+Small sizes of the same commands are what the profiler captures are taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import numpy as np
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        j = json.load(open(p))
+        return float(j["hbm_gbs"]), float(j["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class Timer:
+    """Times `fn` per launch on torch's current stream, which the library is switched to."""
+
+    def __init__(self, gpu, torch):
+        self.gpu, self.torch = gpu, torch
+        self.stream = torch.cuda.Stream()
+        torch.cuda.set_stream(self.stream)
+        gpu.set_stream(self.stream.cuda_stream)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def run(self, fn, iters: int, warmup: int = 3):
+        torch = self.torch
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(iters):
+            self.flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(self.stream)
+            fn()
+            b.record(self.stream)
+            b.synchronize()
+            ms.append(a.elapsed_time(b))
+        self.gpu.sync()
+        return float(np.mean(ms)), float(np.min(ms))
+
+
+def decode(gpu, torch, seqs=256, ctx_lo=512, ctx_hi=2304, heads=32, kv_heads=8, dim=128, iters=20, seed=0):
+    from .gpu import Buf, F32
+    P = 16
+    g = np.random.default_rng(seed)
+    lens = g.integers(ctx_lo, ctx_hi + 1, seqs).astype(np.int32)
+    pages = [-(-int(l) // P) for l in lens]
+    NP, MP = sum(pages) + 3, max(pages)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    kc = torch.empty((NP, P, kv_heads, dim), dtype=torch.float16, device="cuda").normal_(generator=gen)
+    vc = torch.empty((NP, P, kv_heads, dim), dtype=torch.float16, device="cuda").normal_(generator=gen)
+    q = torch.empty((seqs, heads, dim), dtype=torch.float16, device="cuda").normal_(generator=gen)
+    o = torch.zeros_like(q)
+    perm = g.permutation(NP).astype(np.int32)
+    table = np.zeros((seqs, MP), np.int32)
+    at = 0
+    for b, n in enumerate(pages):
+        table[b, :n] = perm[at:at + n]
+        at += n
+    tb, ln = torch.from_numpy(table).cuda(), torch.from_numpy(lens).cuda()
+    k = gpu.kernel("decode_attention", [list(q.shape), list(kc.shape), list(vc.shape), list(tb.shape), [seqs],
+                                        list(q.shape)])
+    args = [Buf(t.data_ptr(), t.numel() * t.element_size()) for t in (q, kc, vc, tb, ln, o)] + [F32(1 / math.sqrt(dim))]
+    t = Timer(gpu, torch)
+    mean, best = t.run(lambda: gpu.launch(k, args), iters)
+    kv = 4.0 * kv_heads * dim * float(lens.sum())
+    nbytes = kv + 4.0 * seqs * heads * dim + 4.0 * sum(pages) + 4.0 * seqs
+    hbm, _, kind = _peaks()
+    gbs = nbytes / (mean * 1e-3) / 1e9
+    return {"kernel": "decode_attention", "seqs": seqs, "ctx": [ctx_lo, ctx_hi], "heads": heads, "kv_heads": kv_heads,
+            "head_dim": dim, "ms": mean, "ms_min": best, "algorithmic_bytes": nbytes, "gbs": gbs, "peak_gbs": hbm,
+            "frac": gbs / hbm, "peak_kind": kind, "device_bytes": int(kc.numel() * 4)}
+
+
+def gemm(gpu, torch, m=4096, n=4096, k=4096, kind="matmul", iters=20, seed=0):
+    from .gpu import Buf
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+
+    def u(*shape, scale=1.0):
+        return (torch.rand(shape, dtype=torch.float32, device="cuda", generator=gen) * 2 - 1).mul_(scale).half()
+
+    buf = lambda t: Buf(t.data_ptr(), t.numel() * t.element_size())
+    a = u(m, k)
+    if kind == "matmul":
+        b, c = u(k, n), torch.zeros((m, n), dtype=torch.float16, device="cuda")
+        kern, args, nb = gpu.kernel("matmul", [[m, k], [k, n], [m, n]]), [buf(a), buf(b), buf(c)], 1
+        out_bytes = 2
+    elif kind == "gate_up":
+        b, b2 = u(n, k, scale=0.05), u(n, k, scale=0.05)
+        c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+        kern = gpu.kernel("gate_up", [[m, k], [n, k], [n, k], [m, n]])
+        args, nb, out_bytes = [buf(a), buf(b), buf(b2), buf(c)], 2, 2
+    else:
+        b = u(n, k, scale=0.05)
+        f32 = kind in ("linear_residual", "logits", "linear_f32")
+        c = torch.zeros((m, n), dtype=torch.float32 if f32 else torch.float16, device="cuda")
+        kern, args, nb = gpu.kernel(kind, [[m, k], [n, k], [m, n]]), [buf(a), buf(b), buf(c)], 1
+        out_bytes = (8 if kind == "linear_residual" else 4) if f32 else 2
+    t = Timer(gpu, torch)
+    mean, best = t.run(lambda: gpu.launch(kern, args), iters)
+    flops = 2.0 * m * n * k * nb
+    nbytes = 2.0 * (m * k + nb * k * n) + out_bytes * m * n
+    hbm, tf, kindp = _peaks()
+    return {"kernel": kind, "m": m, "n": n, "k": k, "ms": mean, "ms_min": best, "flops": flops,
+            "algorithmic_bytes": nbytes, "tflops": flops / (mean * 1e-3) / 1e12, "peak_tflops": tf,
+            "frac_tensor": flops / (mean * 1e-3) / 1e12 / tf, "gbs": nbytes / (mean * 1e-3) / 1e9,
+            "frac_hbm": nbytes / (mean * 1e-3) / 1e9 / hbm, "peak_kind": kindp}
+
+
+def flash(gpu, torch, heads=256, seq=4096, dim=128, iters=10, seed=0):
+    from .gpu import Buf, F32
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    q, k, v = (torch.empty((heads, seq, dim), dtype=torch.float16, device="cuda").normal_(generator=gen)
+               for _ in range(3))
+    o = torch.zeros_like(q)
+    kern = gpu.kernel("flash_attention", [list(q.shape)] * 4)
+    args = [Buf(t.data_ptr(), t.numel() * t.element_size()) for t in (q, k, v, o)] + [F32(1 / math.sqrt(dim))]
+    t = Timer(gpu, torch)
+    mean, best = t.run(lambda: gpu.launch(kern, args), iters)
+    flops = 2.0 * 2.0 * heads * seq * seq * dim / 2.0
+    nbytes = 2.0 * 4.0 * heads * seq * dim
+    _, tf, kindp = _peaks()
+    return {"kernel": "flash_attention", "heads": heads, "seq": seq, "head_dim": dim, "ms": mean, "ms_min": best,
+            "flops": flops, "algorithmic_bytes": nbytes, "tflops": flops / (mean * 1e-3) / 1e12, "peak_tflops": tf,
+            "frac_tensor": flops / (mean * 1e-3) / 1e12 / tf, "peak_kind": kindp}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    d = sub.add_parser("decode")
+    for name, default in (("seqs", 256), ("ctx-lo", 512), ("ctx-hi", 2304), ("heads", 32), ("kv-heads", 8),
+                          ("dim", 128), ("iters", 20)):
+        d.add_argument("--" + name, type=int, default=default)
+    gm = sub.add_parser("gemm")
+    for name, default in (("m", 4096), ("n", 4096), ("k", 4096), ("iters", 20)):
+        gm.add_argument("--" + name, type=int, default=default)
+    gm.add_argument("--kind", default="matmul")
+    f = sub.add_parser("flash")
+    for name, default in (("heads", 256), ("seq", 4096), ("dim", 128), ("iters", 10)):
+        f.add_argument("--" + name, type=int, default=default)
+    a = ap.parse_args()
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a B200: there is no CPU path")
+    from .gpu import Gpu
+    gpu = Gpu(0)
+    if a.cmd == "decode":
+        r = decode(gpu, torch, a.seqs, a.ctx_lo, a.ctx_hi, a.heads, a.kv_heads, a.dim, a.iters)
+    elif a.cmd == "gemm":
+        r = gemm(gpu, torch, a.m, a.n, a.k, a.kind, a.iters)
+    else:
+        r = flash(gpu, torch, a.heads, a.seq, a.dim, a.iters)
+    print(json.dumps(r), flush=True)
+
+
+if __name__ == "__main__":
+    main()
