@@ -6,15 +6,27 @@
 //   matmul           C f16 = A B, B [K,N] row-major    kernels/matmul.tl:3-17
 //   linear_f32       Y f32 = X W^T (a tensor-parallel partial; no counterpart)
 //
-// One CTA computes a 128 x BN tile of the output. Warp 0 streams 64-wide K
-// slices of both operands into a shared-memory ring with TMA (128-byte
-// swizzle); one thread of warp 1 issues tcgen05.mma (M = 128, N = BN or 2 BN,
-// K = 16, f16 in, f32 accumulate) into tensor memory and releases ring slots
-// with tcgen05.commit; warps 2-5 read the finished accumulator out of tensor
-// memory (one row per thread) and apply the epilogue. gate_up loads the Wg and
-// Wu tiles side by side so that one MMA of N = 2 BN produces both products
-// from one read of X. Rows beyond M and columns beyond N are zero-filled by
-// TMA on the way in and masked on the way out.
+// One CTA computes a (MT x 128) x BN tile of the output, MT in {1, 2}. Warp 0
+// streams 64-wide K slices of both operands into a shared-memory ring with TMA
+// (128-byte swizzle); one thread of warp 1 issues tcgen05.mma (M = 128, N = BN
+// or 2 BN, K = 16, f16 in, f32 accumulate) into tensor memory - with MT = 2 two
+// accumulators share every weight tile - and releases ring slots with
+// tcgen05.commit; warps 2-5 read the finished accumulators out of tensor memory
+// (one row per thread) and apply the epilogue. gate_up loads the Wg and Wu
+// tiles side by side so that one MMA of N = 2 BN produces both products from
+// one read of X. Rows beyond M and columns beyond N are zero-filled by TMA on
+// the way in and masked on the way out.
+//
+// The feed from L2 into an SM (about 90 GB/s) is what bounds these kernels
+// before HBM or the tensor pipe does, so tiles are as large as the shape
+// allows: a decode step's 256 rows are ONE CTA's rows, each weight tile is
+// fetched by one CTA only. Projections with few column tiles (QKV, o_proj,
+// down_proj at decode sizes) would then leave SMs idle, so they split K over a
+// thread-block cluster: each CTA accumulates a K range, the partial tiles are
+// exchanged through distributed shared memory (every CTA owns a share of the
+// tile's 128 x 32 units, the others store their partials of those units into
+// its shared memory), and the owner adds them in rank order - a fixed order,
+// so results do not depend on timing - before the epilogue.
 //
 // Shapes whose row pitch is not a multiple of 16 bytes (which TMA cannot
 // address) take a plain tiled CUDA-core kernel with the same epilogues.
@@ -28,38 +40,107 @@ enum Epi : int { EPI_F16 = 0, EPI_RESID = 1, EPI_F32 = 2, EPI_GATE_UP = 3 };
 
 constexpr int BM = 128, BK = 64;
 constexpr int GEMM_THREADS = 192;
+constexpr int UNIT_BYTES = 128 * 32 * 4;  // one 128-row x 32-column f32 unit of a partial tile
+
+#ifdef TB200_TRACE
+__device__ unsigned long long* g_trace = nullptr;  // [CTA][16] timestamps (ns), development builds only
+#define TB_TRACE(point)                                                                              \
+  do {                                                                                               \
+    if (g_trace)                                                                                     \
+      g_trace[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * 16 + (point)] = globaltimer(); \
+  } while (0)
+#else
+#define TB_TRACE(point) \
+  do {                  \
+  } while (0)
+#endif
 
 struct GemmParams {
   void* out;
-  int M, N, K;
+  int M, N, K, splits;
   unsigned int* status;
 };
 
-template <int BN, int EPI>
+template <int MT, int BN, int EPI>
 struct GemmCfg {
   static constexpr int NB = EPI == EPI_GATE_UP ? 2 * BN : BN;  // B rows per stage = MMA N
-  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int A_BYTES = MT * BM * BK * 2;
   static constexpr int B_BYTES = NB * BK * 2;
   static constexpr int STAGE = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (200 * 1024) / STAGE > 8 ? 8 : (200 * 1024) / STAGE;
-  static constexpr int TMEM_COLS = NB <= 32 ? 32 : NB <= 64 ? 64 : NB <= 128 ? 128 : NB <= 256 ? 256 : 512;
+  static constexpr int STAGES = (196 * 1024) / STAGE > 8 ? 8 : (196 * 1024) / STAGE;
+  static constexpr int COLS = MT * NB;
+  static constexpr int TMEM_COLS = COLS <= 32 ? 32 : COLS <= 64 ? 64 : COLS <= 128 ? 128 : COLS <= 256 ? 256 : 512;
   static constexpr int BAR_OFF = STAGES * STAGE;
   static constexpr int SMEM = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;
-  static_assert(NB % 16 == 0 && NB <= 256, "UMMA N");
+  static constexpr int UNITS = MT * (BN / 32);
+  static_assert(NB % 16 == 0 && NB <= 256 && COLS <= 512, "UMMA N / TMEM columns");
+  static_assert(STAGES >= 2, "ring too shallow");
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
-  // g / (1 + exp(-g)) * u with each step rounded, as kernels/llm.tl:73 evaluates it.
+  // g / (1 + exp(-g)) * u (kernels/llm.tl:73) on the fast exponential and division units:
+  // a few f32 ulps from the interpreter's op-by-op rounding, far inside the f16 output step.
+#ifdef TB200_EXACT_SILU
   const float e = expf(-g);
   return __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, e)), u);
+#else
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+#endif
+}
+
+// Writes 32 consecutive columns of one output row (col0 .. col0 + 31, clipped to N).
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col0, const float* v) {
+  if (row >= p.M || col0 >= p.N) return;
+  const bool fullw = col0 + 32 <= p.N && (p.N % 8) == 0;
+  if (EPI == EPI_F16 || EPI == EPI_GATE_UP) {
+    __half* y = (__half*)p.out + (size_t)row * p.N + col0;
+    if (fullw) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint4 o;
+        o.x = pack_h2(v[j], v[j + 1]);
+        o.y = pack_h2(v[j + 2], v[j + 3]);
+        o.z = pack_h2(v[j + 4], v[j + 5]);
+        o.w = pack_h2(v[j + 6], v[j + 7]);
+        *reinterpret_cast<uint4*>(y + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) y[j] = __float2half_rn(v[j]);
+    }
+  } else {
+    float* y = (float*)p.out + (size_t)row * p.N + col0;
+    if (fullw) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4) {
+        float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        if (EPI == EPI_RESID) {
+          const float4 old = *reinterpret_cast<const float4*>(y + j);
+          o.x = __fadd_rn(old.x, o.x);
+          o.y = __fadd_rn(old.y, o.y);
+          o.z = __fadd_rn(old.z, o.z);
+          o.w = __fadd_rn(old.w, o.w);
+        }
+        *reinterpret_cast<float4*>(y + j) = o;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N) y[j] = EPI == EPI_RESID ? __fadd_rn(y[j], v[j]) : v[j];
+    }
+  }
 }
 
 // B_MN: B is a [K, N] row-major array (N-major operand); else W [N, K] (K-major).
-template <int BN, int EPI, bool B_MN>
+// Grid: (row tiles, column tiles, K splits); with splits > 1 the launch carries a
+// cluster of (1, 1, splits).
+template <int MT, int BN, int EPI, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                 const __grid_constant__ CUtensorMap mapB2, const GemmParams p) {
-  using Cfg = GemmCfg<BN, EPI>;
+  using Cfg = GemmCfg<MT, BN, EPI>;
   constexpr int NB = Cfg::NB, STAGES = Cfg::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -69,10 +150,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int m0 = blockIdx.x * (MT * BM), n0 = blockIdx.y * BN;
   const int nk = (p.K + BK - 1) / BK;
+  const int S = p.splits;
+  const int k_begin = (int)((long long)nk * blockIdx.z / S), k_end = (int)((long long)nk * (blockIdx.z + 1) / S);
+  const int niter = k_end - k_begin;  // >= 1: the host never asks for more splits than K blocks
 
   if (threadIdx.x == 0) {
+    TB_TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -94,103 +179,152 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       prefetch_tmap(&mapA);
       prefetch_tmap(&mapB);
       if (EPI == EPI_GATE_UP) prefetch_tmap(&mapB2);
-      for (int i = 0; i < nk; ++i) {
-        const int s = i % STAGES, k = i / STAGES;
+      TB_TRACE(1);
+      for (int i = 0; i < niter; ++i) {
+        const int s = i % STAGES, k = i / STAGES, kc = (k_begin + i) * BK;
         mbar_wait(&empty[s], (k & 1) ^ 1, p.status, 201);
         mbar_expect_tx(&full[s], Cfg::STAGE);
         unsigned char* a = smem + s * Cfg::STAGE;
         unsigned char* b = a + Cfg::A_BYTES;
-        tma_load_2d(a, &mapA, &full[s], i * BK, m0);
+        tma_load_2d(a, &mapA, &full[s], kc, m0);
         if (B_MN) {
           // 64-column blocks of [64 k-rows x 128 bytes] each.
 #pragma unroll
-          for (int nb = 0; nb < BN / 64; ++nb) tma_load_2d(b + nb * (BK * 128), &mapB, &full[s], n0 + nb * 64, i * BK);
+          for (int nb = 0; nb < BN / 64; ++nb) tma_load_2d(b + nb * (BK * 128), &mapB, &full[s], n0 + nb * 64, kc);
         } else {
-          tma_load_2d(b, &mapB, &full[s], i * BK, n0);
-          if (EPI == EPI_GATE_UP) tma_load_2d(b + BN * BK * 2, &mapB2, &full[s], i * BK, n0);
+          tma_load_2d(b, &mapB, &full[s], kc, n0);
+          if (EPI == EPI_GATE_UP) tma_load_2d(b + BN * BK * 2, &mapB2, &full[s], kc, n0);
         }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc = umma_idesc_f16(BM, NB, 0, B_MN ? 1 : 0);
-      for (int i = 0; i < nk; ++i) {
+      for (int i = 0; i < niter; ++i) {
         const int s = i % STAGES, k = i / STAGES;
         mbar_wait(&full[s], k & 1, p.status, 202);
+        if (i == 0) TB_TRACE(2);
         tc_fence_after();
         const uint32_t a = smem_u32(smem + s * Cfg::STAGE);
         const uint32_t b = a + Cfg::A_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BK / 16; ++kk) {
-          const uint64_t ad = umma_desc_sw128(a + kk * 32, 16, 1024);
           const uint64_t bd = B_MN ? umma_desc_sw128(b + kk * 2048, BK * 128, 1024)
                                    : umma_desc_sw128(b + kk * 32, 16, 1024);
-          umma_f16(tmem, ad, bd, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint64_t ad = umma_desc_sw128(a + mt * (BM * 128) + kk * 32, 16, 1024);
+            umma_f16(tmem + mt * NB, ad, bd, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&empty[s]);  // frees the slot once these MMAs have read it
       }
+      TB_TRACE(3);
       umma_commit(acc_full);
     }
-  } else {
-    // ---- epilogue: 4 warps, TMEM lane quadrant = warp % 4 ------------------
-    const int q = warp & 3;
-    const int row = m0 + q * 32 + lane;
+  }
+
+  // ---- epilogue: warps 2-5, TMEM lane quadrant = warp % 4, one output row per thread ----
+  const bool epi = warp >= 2;
+  const int q = warp & 3;
+  const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+  const bool tracer = warp == 2 && lane == 0;
+  if (epi) {
     mbar_wait(acc_full, 0, p.status, 203);
     tc_fence_after();
-    const bool row_ok = row < p.M;
-    const bool vec_ok = (p.N % 8) == 0;
+    if (tracer) TB_TRACE(4);
+  }
+  if (S == 1) {
+    if (epi) {
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + c0, r);
-      uint32_t r2[32];
-      if (EPI == EPI_GATE_UP) tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + BN + c0, r2);
-      tmem_ld_wait();
-      const int col = n0 + c0;
-      if (!row_ok || col >= p.N) continue;
-      const bool fullw = col + 32 <= p.N && vec_ok;
-      if (EPI == EPI_F16 || EPI == EPI_GATE_UP) {
-        __half* y = (__half*)p.out + (size_t)row * p.N + col;
-        float v[32];
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row = m0 + mt * BM + q * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          float v[32];
+          tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+          if (EPI == EPI_GATE_UP) {
+            uint32_t r2[32];
+            tmem_ld32(tmem + lane_base + mt * NB + BN + c0, r2);
+            tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          v[j] = EPI == EPI_GATE_UP ? silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j])) : __uint_as_float(r[j]);
-        if (fullw) {
+            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j]));
+          } else {
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 o;
-            o.x = pack_h2(v[j], v[j + 1]);
-            o.y = pack_h2(v[j + 2], v[j + 3]);
-            o.z = pack_h2(v[j + 4], v[j + 5]);
-            o.w = pack_h2(v[j + 6], v[j + 7]);
-            *reinterpret_cast<uint4*>(y + j) = o;
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           }
-        } else {
-          for (int j = 0; j < 32 && col + j < p.N; ++j) y[j] = __float2half_rn(v[j]);
-        }
-      } else {
-        float* y = (float*)p.out + (size_t)row * p.N + col;
-        if (fullw) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                   __uint_as_float(r[j + 3]));
-            if (EPI == EPI_RESID) {
-              const float4 old = *reinterpret_cast<const float4*>(y + j);
-              o.x = __fadd_rn(old.x, o.x);
-              o.y = __fadd_rn(old.y, o.y);
-              o.z = __fadd_rn(old.z, o.z);
-              o.w = __fadd_rn(old.w, o.w);
-            }
-            *reinterpret_cast<float4*>(y + j) = o;
-          }
-        } else {
-          for (int j = 0; j < 32 && col + j < p.N; ++j)
-            y[j] = EPI == EPI_RESID ? __fadd_rn(y[j], __uint_as_float(r[j])) : __uint_as_float(r[j]);
+          store_chunk<EPI>(p, row, n0 + c0, v);
         }
       }
     }
+  } else {
+    // Split K: exchange partial tiles through distributed shared memory.
+    constexpr int CH = BN / 32;
+    const int per = Cfg::UNITS / S;  // units each CTA owns (the host picks S dividing UNITS)
+    const uint32_t crank = cluster_ctarank();
+    __syncwarp();
+    cluster_sync();  // every CTA of the cluster has finished its MMAs: all rings are free
+    if (tracer) TB_TRACE(5);
+    float* recv = (float*)smem;  // [(S - 1) senders][per][8 float4 columns][128 rows]
+    const int rit = q * 32 + lane;  // row within the 128-row unit
+    if (epi) {
+      for (int u = 0; u < Cfg::UNITS; ++u) {
+        const uint32_t owner = (uint32_t)(u % S);
+        if (owner == crank) continue;
+        const int mt = u / CH, c0 = (u % CH) * 32;
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+        tmem_ld_wait();
+        const uint32_t sidx = crank < owner ? crank : crank - 1;  // my place among the owner's senders
+        const uint32_t local = smem_u32(recv) + (sidx * per + u / S) * UNIT_BYTES + rit * 16;
+        const uint32_t remote = cluster_map(local, owner);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          st_cluster_f4(remote + j * 2048, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+      }
+    }
+    if (tracer) TB_TRACE(6);
+    __syncwarp();
+    cluster_sync();  // all partials have landed
+    if (tracer) TB_TRACE(7);
+    if (epi) {
+      for (int slot = 0; slot < per; ++slot) {
+        const int u = slot * S + (int)crank;
+        const int mt = u / CH, c0 = (u % CH) * 32;
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+        tmem_ld_wait();
+        float v[32];
+        // Partials are added in rank order 0, 1, ..., S-1 whatever the timing.
+        for (int s = 0; s < S; ++s) {
+          if ((uint32_t)s == crank) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = s == 0 ? __uint_as_float(r[j]) : __fadd_rn(v[j], __uint_as_float(r[j]));
+          } else {
+            const int sidx = (uint32_t)s < crank ? s : s - 1;
+            const float4* src = (const float4*)((const unsigned char*)recv + (sidx * per + slot) * UNIT_BYTES) + rit;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 t = src[j * 128];
+              if (s == 0) {
+                v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
+              } else {
+                v[4 * j] = __fadd_rn(v[4 * j], t.x);
+                v[4 * j + 1] = __fadd_rn(v[4 * j + 1], t.y);
+                v[4 * j + 2] = __fadd_rn(v[4 * j + 2], t.z);
+                v[4 * j + 3] = __fadd_rn(v[4 * j + 3], t.w);
+              }
+            }
+          }
+        }
+        store_chunk<EPI>(p, m0 + mt * BM + rit, n0 + c0, v);
+      }
+    }
   }
+  if (tracer) TB_TRACE(8);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -264,20 +398,34 @@ GemmShape gemm_shape(const Op& op) {
   return g;
 }
 
-template <int BN, int EPI, bool B_MN>
-int set_attr(Ctx* c) {
-  TB_CUDA(c, cudaFuncSetAttribute(gemm_kernel<BN, EPI, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  GemmCfg<BN, EPI>::SMEM));
-  return 0;
+int epi_of(Kind k) {
+  switch (k) {
+    case K_LINEAR:
+    case K_MATMUL:
+      return EPI_F16;
+    case K_LINEAR_RESIDUAL:
+      return EPI_RESID;
+    case K_GATE_UP:
+      return EPI_GATE_UP;
+    default:
+      return EPI_F32;
+  }
 }
 
-template <int BN, int EPI, bool B_MN>
-int run(Ctx* c, const GemmShape& g, const void* A, const void* B, const void* B2, void* out) {
+template <int MT, int BN, int EPI, bool B_MN>
+int run(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, const void* B2, void* out,
+        bool attr_only) {
+  using Cfg = GemmCfg<MT, BN, EPI>;
+  if (attr_only) {
+    TB_CUDA(c, cudaFuncSetAttribute(gemm_kernel<MT, BN, EPI, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::SMEM));
+    return 0;
+  }
   CUtensorMap ma, mb, mb2;
   {
     const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
     const uint64_t strides[1] = {(uint64_t)g.K * 2};
-    const uint32_t box[2] = {BK, BM};
+    const uint32_t box[2] = {BK, MT * BM};
     if (make_tensor_map(c, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, dims, strides, box,
                         CU_TENSOR_MAP_SWIZZLE_128B))
       return 1;
@@ -308,10 +456,21 @@ int run(Ctx* c, const GemmShape& g, const void* A, const void* B, const void* B2
   p.M = g.M;
   p.N = g.N;
   p.K = g.K;
+  p.splits = splits;
   p.status = c->status;
-  dim3 grid((g.M + BM - 1) / BM, (g.N + BN - 1) / BN);
-  gemm_kernel<BN, EPI, B_MN><<<grid, GEMM_THREADS, GemmCfg<BN, EPI>::SMEM, c->stream>>>(ma, mb, mb2, p);
-  TB_CUDA(c, cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((g.M + MT * BM - 1) / (MT * BM), (g.N + BN - 1) / BN, splits);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 1;
+  at[0].val.clusterDim.y = 1;
+  at[0].val.clusterDim.z = splits;
+  cfg.attrs = at;
+  cfg.numAttrs = splits > 1 ? 1 : 0;
+  TB_CUDA(c, cudaLaunchKernelEx(&cfg, gemm_kernel<MT, BN, EPI, B_MN>, ma, mb, mb2, p));
   return 0;
 }
 
@@ -324,23 +483,89 @@ int run_plain(Ctx* c, const GemmShape& g, const void* A, const void* B, const vo
   return 0;
 }
 
-int epi_of(Kind k) {
-  switch (k) {
-    case K_LINEAR:
-    case K_MATMUL:
-      return EPI_F16;
-    case K_LINEAR_RESIDUAL:
-      return EPI_RESID;
-    case K_GATE_UP:
-      return EPI_GATE_UP;
-    default:
-      return EPI_F32;
+// The instantiated tiles. gate_up: BN <= 128 (its MMA is 2 BN wide); matmul: BN >= 64.
+template <int MT, int BN>
+int dispatch_epi(Ctx* c, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
+                 void* out, bool attr_only) {
+  const int epi = epi_of(kind);
+  if (kind == K_MATMUL) {
+    if constexpr (BN >= 64 && BN != 192) return run<MT, BN, EPI_F16, true>(c, g, splits, A, B, B2, out, attr_only);
+  } else if (epi == EPI_GATE_UP) {
+    if constexpr (BN <= 128) return run<MT, BN, EPI_GATE_UP, false>(c, g, splits, A, B, B2, out, attr_only);
+  } else if (epi == EPI_F16) {
+    return run<MT, BN, EPI_F16, false>(c, g, splits, A, B, B2, out, attr_only);
+  } else if (epi == EPI_RESID) {
+    return run<MT, BN, EPI_RESID, false>(c, g, splits, A, B, B2, out, attr_only);
+  } else {
+    return run<MT, BN, EPI_F32, false>(c, g, splits, A, B, B2, out, attr_only);
   }
+  return fail(c, "gemm: tile not instantiated for this kernel");
+}
+
+int dispatch(Ctx* c, Kind kind, int mt, int bn, const GemmShape& g, int splits, const void* A, const void* B,
+             const void* B2, void* out, bool attr_only) {
+#define TB_CASE(MT_, BN_) \
+  if (mt == MT_ && bn == BN_) return dispatch_epi<MT_, BN_>(c, kind, g, splits, A, B, B2, out, attr_only);
+  TB_CASE(1, 32) TB_CASE(1, 64) TB_CASE(1, 128) TB_CASE(1, 256)
+  TB_CASE(2, 32) TB_CASE(2, 64) TB_CASE(2, 128) TB_CASE(2, 192) TB_CASE(2, 256)
+#undef TB_CASE
+  return fail(c, "gemm: no such tile");
+}
+
+struct Plan {
+  int mt, bn, splits;
+  double t;
+};
+
+// Picks (MT, BN, splits) by a small cost model: waves of CTAs over the SMs, each CTA bound by
+// the slower of its L2-to-SM feed and its MMAs, plus its epilogue (and the partial exchange).
+Plan plan_gemm(Kind kind, const GemmShape& g, int sms) {
+  const double FEED = 90e9, TENSOR = 1636e12 / 148.0, HBM = 6.5e12;
+  const int nk = (g.K + BK - 1) / BK;
+  const int epi = epi_of(kind);
+  const int out_bytes = epi == EPI_RESID ? 8 : (epi == EPI_F32 ? 4 : 2);
+  const int nbf = epi == EPI_GATE_UP ? 2 : 1;
+  const int bns[] = {256, 192, 128, 64, 32};
+  Plan best = {1, 64, 1, 1e30};
+  for (int mt = 1; mt <= 2; ++mt) {
+    if (mt == 2 && g.M <= BM) continue;
+    for (int bn : bns) {
+      if (kind == K_MATMUL && (bn < 64 || bn == 192)) continue;
+      if (epi == EPI_GATE_UP && bn > 128) continue;
+      if (bn == 192 && mt == 1) continue;
+      const int nb = bn * nbf;
+      if (mt * nb > 512) continue;
+      const int stage = mt * BM * BK * 2 + nb * BK * 2;
+      int stages = (196 * 1024) / stage;
+      if (stages > 8) stages = 8;
+      if (stages < 2) continue;
+      for (int s = 1; s <= 4; s *= 2) {
+        const int units = mt * (bn / 32);
+        if (s > 1) {
+          if (epi == EPI_GATE_UP || nk < 8 * s || units % s) continue;
+          if ((s - 1) * (units / s) * UNIT_BYTES > stages * stage) continue;
+        }
+        const long long mtiles = (g.M + mt * BM - 1) / (mt * BM), ntiles = (g.N + bn - 1) / bn;
+        const long long ctas = mtiles * ntiles * s;
+        const long long waves = (ctas + sms - 1) / sms;
+        const double kiter = (double)((nk + s - 1) / s);
+        const double t_feed = kiter * stage / FEED;
+        const double t_mma = kiter * (2.0 * mt * BM * nb * BK) / TENSOR;
+        double t_epi = (double)mt * BM * bn * out_bytes / FEED;
+        if (s > 1) t_epi += 2.0e-6 + 2.0 * (s - 1) / s * mt * BM * bn * 4 / FEED;
+        double t = waves * ((t_feed > t_mma ? t_feed : t_mma) + 1.5e-6 + t_epi);
+        const double floor_t = (2.0 * g.M * g.K + 2.0 * nbf * (double)g.N * g.K + (double)out_bytes * g.M * g.N) / HBM;
+        if (t < floor_t) t = floor_t;
+        if (t < best.t) best = {mt, bn, s, t};
+      }
+    }
+  }
+  return best;
 }
 
 }  // namespace
 
-// op.p0: 1 = tcgen05 path, 0 = plain path. op.p1: BN.
+// op.p0: 1 = tcgen05 path, 0 = plain path, -1 = nothing to do. op.p1 = MT, p2 = BN, p3 = splits.
 int make_gemm(Ctx* c, Op& op) {
   const auto& s = op.shapes;
   auto bad = [&](const char* why) { return fail(c, op.name + ": " + why); };
@@ -356,56 +581,27 @@ int make_gemm(Ctx* c, Op& op) {
     if (s[1][1] != g.K || s[2][0] != g.M || s[2][1] != g.N) return bad("shapes are X[M,K], W[N,K], Y[M,N]");
   }
   if (g.M == 0 || g.N == 0) {
-    op.p0 = -1;  // nothing to compute
+    op.p0 = -1;
     return 0;
   }
   const bool tma_ok = g.K > 0 && g.K % 8 == 0 && (op.kind != K_MATMUL || g.N % 8 == 0);
   op.p0 = tma_ok ? 1 : 0;
   if (!tma_ok) return 0;
-  // Tile width: wide tiles for prompt-sized M (compute-bound), narrower ones
-  // when few rows leave the kernel bound by streaming the weights and the
-  // grid has to cover the SMs.
-  const int mt = (g.M + BM - 1) / BM;
-  int bn;
-  if (op.kind == K_GATE_UP) {
-    bn = 128;
-    if ((long long)mt * ((g.N + 127) / 128) < c->sm_count) bn = 64;
-    if ((long long)mt * ((g.N + 63) / 64) < c->sm_count) bn = 32;
-  } else if (op.kind == K_MATMUL) {
-    bn = 256;
-    if ((long long)mt * ((g.N + 255) / 256) < c->sm_count) bn = 128;
-    if ((long long)mt * ((g.N + 127) / 128) < c->sm_count) bn = 64;
-  } else {
-    bn = 256;
-    if ((long long)mt * ((g.N + 255) / 256) < c->sm_count) bn = 128;
-    if ((long long)mt * ((g.N + 127) / 128) < c->sm_count) bn = 64;
-    if ((long long)mt * ((g.N + 63) / 64) < c->sm_count) bn = 32;
+  Plan pl = plan_gemm(op.kind, g, c->sm_count);
+  // TB200_GEMM_PLAN="mt,bn,splits" overrides the choice (tuning and tests).
+  if (const char* e = getenv("TB200_GEMM_PLAN")) {
+    int a = 0, b = 0, d = 0;
+    if (sscanf(e, "%d,%d,%d", &a, &b, &d) == 3) {
+      const int nk = (g.K + BK - 1) / BK;
+      const bool ok = (a == 1 || a == 2) && d >= 1 && d <= 8 && d <= nk && (d == 1 || op.kind != K_GATE_UP) &&
+                      (d == 1 || (a * (b / 32)) % d == 0);
+      if (ok) pl = {a, b, d, 0.0};
+    }
   }
-  op.p1 = bn;
-  int r = 0;
-#define TB_ATTR(BN_)                                                        \
-  switch (epi_of(op.kind)) {                                                \
-    case EPI_F16:                                                           \
-      r = op.kind == K_MATMUL ? set_attr<(BN_ < 64 ? 64 : BN_), EPI_F16, true>(c) : set_attr<BN_, EPI_F16, false>(c); \
-      break;                                                                \
-    case EPI_RESID:                                                         \
-      r = set_attr<BN_, EPI_RESID, false>(c);                               \
-      break;                                                                \
-    case EPI_F32:                                                           \
-      r = set_attr<BN_, EPI_F32, false>(c);                                 \
-      break;                                                                \
-    default:                                                                \
-      r = set_attr<(BN_ > 128 ? 128 : BN_), EPI_GATE_UP, false>(c);         \
-      break;                                                                \
-  }
-  switch (bn) {
-    case 32: TB_ATTR(32); break;
-    case 64: TB_ATTR(64); break;
-    case 128: TB_ATTR(128); break;
-    default: TB_ATTR(256); break;
-  }
-#undef TB_ATTR
-  return r;
+  op.p1 = pl.mt;
+  op.p2 = pl.bn;
+  op.p3 = pl.splits;
+  return dispatch(c, op.kind, pl.mt, pl.bn, g, pl.splits, nullptr, nullptr, nullptr, nullptr, true);
 }
 
 int launch_gemm(Ctx* c, Op& op, const uint64_t* a) {
@@ -437,24 +633,7 @@ int launch_gemm(Ctx* c, Op& op, const uint64_t* a) {
     else
       r = run_plain<EPI_GATE_UP, false>(c, g, A, B, B2, out);
   } else {
-#define TB_RUN(BN_)                                                                                  \
-  if (mn)                                                                                            \
-    r = run<(BN_ < 64 ? 64 : BN_), EPI_F16, true>(c, g, A, B, B2, out);                              \
-  else if (epi == EPI_F16)                                                                           \
-    r = run<BN_, EPI_F16, false>(c, g, A, B, B2, out);                                               \
-  else if (epi == EPI_RESID)                                                                         \
-    r = run<BN_, EPI_RESID, false>(c, g, A, B, B2, out);                                             \
-  else if (epi == EPI_F32)                                                                           \
-    r = run<BN_, EPI_F32, false>(c, g, A, B, B2, out);                                               \
-  else                                                                                               \
-    r = run<(BN_ > 128 ? 128 : BN_), EPI_GATE_UP, false>(c, g, A, B, B2, out);
-    switch (op.p1) {
-      case 32: TB_RUN(32); break;
-      case 64: TB_RUN(64); break;
-      case 128: TB_RUN(128); break;
-      default: TB_RUN(256); break;
-    }
-#undef TB_RUN
+    r = dispatch(c, op.kind, op.p1, op.p2, g, op.p3, A, B, B2, out, false);
   }
   if (r) return r;
   c->launches += 1;

@@ -94,6 +94,35 @@ def test_matmul_4096_cubed(gpu):
     assert np.array_equal(c1, (ai.astype(f) @ b1.astype(f)))
 
 
+@pytest.mark.parametrize("plan,M,N,K", [
+    ("1,128,1", 200, 392, 1024), ("2,128,1", 256, 520, 1032), ("2,256,1", 256, 776, 1040),
+    ("2,128,2", 256, 264, 2048), ("2,128,4", 256, 4096, 4096), ("2,192,4", 256, 6144, 4096),
+    ("2,256,4", 250, 1288, 4104), ("2,256,2", 256, 1296, 1096), ("1,128,4", 100, 136, 2056),
+    ("2,64,4", 256, 200, 3080), ("2,128,4", 256, 4104, 14336),
+])
+def test_forced_tiles_and_cluster_split_k(gpu, plan, M, N, K, monkeypatch):
+    """Every tile shape and the cluster split-K exchange (TB200_GEMM_PLAN = MT,BN,splits), on shapes
+    no other test uses (a kernel is made once per shape), for all four epilogues; and the split
+    sum is the same bits on every run (partials are added in rank order)."""
+    monkeypatch.setenv("TB200_GEMM_PLAN", plan)
+    r = oracle.Rng(33)
+    x, w = r.tensor(h, (M, K)), r.tensor(h, (N, K), 0.1)
+    res = r.tensor(f, (M, N))
+    rows = np.unique(np.linspace(0, M - 1, 12).astype(int))
+    y = launch(gpu, "linear", [x, w, np.zeros((M, N), h)], 2)
+    assert rel_err(y[rows], oracle.linear(x[rows], w)) <= TOL
+    y2 = launch(gpu, "linear", [x, w, np.zeros((M, N), h)], 2)
+    assert np.array_equal(y.view(np.uint16), y2.view(np.uint16))
+    y = launch(gpu, "logits", [x, w, np.full((M, N), 3, f)], 2)
+    assert rel_err(y[rows], oracle.logits(x[rows], w)) <= TOL
+    y = launch(gpu, "linear_residual", [x, w, res.copy()], 2)
+    assert rel_err(y[rows], oracle.linear_residual(x[rows], w, res[rows])) <= TOL
+    if plan.endswith(",1") and not plan.startswith("2,256"):
+        wu = r.tensor(h, (N, K), 0.1)
+        y = launch(gpu, "gate_up", [x, w, wu, np.zeros((M, N), h)], 3)
+        assert rel_err(y[rows], oracle.gate_up(x[rows], w, wu)) <= TOL
+
+
 def test_empty_shapes(gpu):
     x = np.zeros((0, 64), h)
     w = np.ones((32, 64), h)
