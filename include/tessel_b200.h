@@ -125,6 +125,26 @@ int tb200_comm_id(tb200_ctx* ctx, void* id_out);
 int tb200_comm_init(tb200_ctx* ctx, int rank, int nranks, const void* id);
 int tb200_allreduce(tb200_ctx* ctx, uint64_t dptr, size_t count, int dtype);
 
+/* No counterpart in the reference. Paged decode attention (the computation of
+ * the "decode_attention" kernel above) for callers that cannot allocate device
+ * memory: a host that gave its whole device-memory budget to its own pool at
+ * start-up, or that must not enter the allocator where it runs. The kernel's
+ * split-KV scratch is a 16 MiB array inside the library image (held by every
+ * GPU that loads the library, until the process exits) instead of an
+ * allocation; this call performs no cudaMalloc / cudaFree.
+ *   dims = {B, H, G, D, NP, P, MP}: Q, O f16 [B,H,D]; Kc, Vc f16 [NP,P,G,D];
+ *   table i32 [B,MP]; lens i32 [B].
+ * Limit: B*H*(D+2)*4 bytes (one split's partials) must fit the 16 MiB, else the
+ * call fails with a message saying so; within the limit the number of KV
+ * splits is reduced to what fits. The first call on a device resolves the
+ * array's device address and sets kernel attributes: make that first call
+ * before any stream capture. All calls on a device share the one array and it
+ * keeps the previous call's contents (nothing in it has to be cleared); two
+ * calls that overlap on the GPU (different streams or contexts) would race on
+ * it, so keep them on one stream. */
+int tb200_decode_attention_static(tb200_ctx* ctx, const int32_t* dims, uint64_t q, uint64_t kc, uint64_t vc,
+                                  uint64_t table, uint64_t lens, uint64_t o, float scale);
+
 /* Host helper: the seeded xorshift generator of src/bench.rs:13-35, as
  * Weights::random (src/llm/mod.rs:80-108) draws from it. `state` starts as
  * tb200_rng_seed(seed). */

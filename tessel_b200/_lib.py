@@ -39,6 +39,9 @@ SYMBOLS = [
     ("tb200_comm_id", C.c_int, [C.c_void_p, C.c_void_p]),
     ("tb200_comm_init", C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
     ("tb200_allreduce", C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_int]),
+    ("tb200_decode_attention_static", C.c_int,
+     [C.c_void_p, C.POINTER(C.c_int32), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
+      C.c_float]),
     ("tb200_rng_seed", C.c_uint64, [C.c_uint64]),
     ("tb200_rng_uniform", None, [_u64p, C.c_void_p, C.c_size_t]),
 ]

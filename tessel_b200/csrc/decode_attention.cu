@@ -449,3 +449,125 @@ int launch_decode(Ctx* c, Op& op, const uint64_t* a) {
 }
 
 }  // namespace tb
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for hosts that must not allocate device memory.
+//
+// tb200_kernel("decode_attention", ...) sizes and cudaMallocs the split-KV scratch when the op is
+// made. Some callers cannot do that: a serving process whose whole device-memory budget was
+// handed to its own pool at start-up (so any later cudaMalloc fails or fragments it), code that
+// runs inside a region where the allocator must not be entered (a captured stream, a real-time
+// thread), or a host that is simply forbidden to allocate after initialisation. For them the
+// scratch below lives in the library image itself: every GPU that loads the library holds these
+// 16 MiB until the process exits, and this entry point uses them instead of an allocation.
+// ---------------------------------------------------------------------------------------------
+#define TB200_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_decode_static_scratch[TB200_STATIC_SCRATCH_BYTES];
+
+namespace tb {
+namespace {
+constexpr int MAX_DEVICES = 64;
+// Device address of g_decode_static_scratch on each device, resolved on the first call there.
+float* g_static_scratch_addr[MAX_DEVICES] = {};
+}  // namespace
+}  // namespace tb
+
+struct tb200_ctx {
+  tb::Ctx c;
+};
+
+extern "C" int tb200_decode_attention_static(tb200_ctx* h, const int32_t* dims, uint64_t q, uint64_t kc, uint64_t vc,
+                                             uint64_t table, uint64_t lens, uint64_t o, float scale) {
+  using namespace tb;
+  Ctx* c = &h->c;
+  if (!dims) return fail(c, "tb200_decode_attention_static: dims is NULL");
+  DecodeShape d;
+  d.B = dims[0], d.H = dims[1], d.G = dims[2], d.D = dims[3], d.NP = dims[4], d.P = dims[5], d.MP = dims[6];
+  if (d.B < 0 || d.H < 1 || d.G < 1 || d.H % d.G || d.NP < 0 || d.P < 1 || d.MP < 0)
+    return fail(c, "tb200_decode_attention_static: dims are B, H, G, D, NP, P, MP with H a multiple of G");
+  if (d.D % 8 || d.D < 8 || d.D > 256)
+    return fail(c, "tb200_decode_attention_static: head_dim must be a multiple of 8, at most 256");
+  if (d.B == 0) return 0;
+  const bool fast = d.P == 16 && (d.D == 64 || d.D == 128) && d.NP > 0 && d.MP > 0;
+  if (!fast) {
+    // The one-warp-per-head kernel keeps everything in registers: it has no scratch at all.
+    const int warps = d.B * d.H;
+    decode_generic_kernel<<<(warps + 3) / 4, 128, 0, c->stream>>>((const __half*)q, (const __half*)kc,
+                                                                  (const __half*)vc, (const int*)table,
+                                                                  (const int*)lens, (__half*)o, scale, d.B, d.H, d.G,
+                                                                  d.D, d.NP, d.P, d.MP);
+    TB_CUDA(c, cudaGetLastError());
+    c->launches += 1;
+    return 0;
+  }
+  if (c->device < 0 || c->device >= MAX_DEVICES) return fail(c, "tb200_decode_attention_static: device index too large");
+  // Set-up, once per device, with that device current. The array's name is only a host-side
+  // handle for the symbol; the address a kernel may use comes from cudaGetSymbolAddress.
+  TB_CUDA(c, cudaSetDevice(c->device));
+  if (!g_static_scratch_addr[c->device]) {
+    void* ptr = nullptr;
+    TB_CUDA(c, cudaGetSymbolAddress(&ptr, g_decode_static_scratch));
+    if (!ptr) return fail(c, "tb200_decode_attention_static: the scratch symbol has no device address");
+    TB_CUDA(c, cudaFuncSetAttribute(decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    DecSmem<128>::TOTAL));
+    TB_CUDA(c, cudaFuncSetAttribute(decode_tma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    DecSmem<64>::TOTAL));
+    g_static_scratch_addr[c->device] = (float*)ptr;
+  }
+  // As many KV splits as the scratch can hold partials for, up to what fills the SMs.
+  const size_t per_split = (size_t)d.B * d.H * (d.D + 2) * sizeof(float);
+  if (per_split > TB200_STATIC_SCRATCH_BYTES) {
+    char msg[256];
+    snprintf(msg, sizeof msg,
+             "tb200_decode_attention_static: B*H*(D+2)*4 = %zu bytes of partials exceed the %u-byte static scratch "
+             "(B %d, H %d, D %d); use tb200_kernel(\"decode_attention\") instead",
+             per_split, TB200_STATIC_SCRATCH_BYTES, d.B, d.H, d.D);
+    return fail(c, msg);
+  }
+  const int hgroups = (d.H / d.G + 7) / 8;
+  const long long units = (long long)d.B * d.G * hgroups;
+  long long want = (4LL * c->sm_count + units - 1) / units;
+  const long long fit = (long long)(TB200_STATIC_SCRATCH_BYTES / per_split);
+  const int max_split = (d.MP + 3) / 4;
+  if (want > fit) want = fit;
+  int nsplit = (int)(want < 1 ? 1 : (want > max_split ? max_split : want));
+  int chunk = (d.MP + nsplit - 1) / nsplit;
+  chunk = (chunk + 3) / 4 * 4;
+  nsplit = (d.MP + chunk - 1) / chunk;
+  const int SUB = d.D / 64;
+  CUtensorMap mk, mv;
+  const uint64_t tdims[4] = {64, (uint64_t)SUB * d.G, (uint64_t)d.P, (uint64_t)d.NP};
+  const uint64_t strides[3] = {128, (uint64_t)d.G * d.D * 2, (uint64_t)d.P * d.G * d.D * 2};
+  const uint32_t box[4] = {64, 1, 16, 1};
+  if (make_tensor_map(c, &mk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (const void*)kc, tdims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+    return 1;
+  if (make_tensor_map(c, &mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (const void*)vc, tdims, strides, box,
+                      CU_TENSOR_MAP_SWIZZLE_128B))
+    return 1;
+  DecodeParams p;
+  p.Q = (const __half*)q;
+  p.table = (const int*)table;
+  p.lens = (const int*)lens;
+  p.O = (__half*)o;
+  p.scale = scale;
+  p.B = d.B, p.H = d.H, p.G = d.G, p.NP = d.NP, p.MP = d.MP;
+  p.chunk = chunk;
+  p.nsplit = nsplit;
+  // Nothing in the scratch has to start at zero: every partial the merge reads was written by
+  // this call's first kernel (the merge derives the live splits from lens, as the writers do).
+  p.part_acc = g_static_scratch_addr[c->device];
+  p.part_ml = p.part_acc + (size_t)d.B * d.H * nsplit * d.D;
+  p.status = c->status;
+  dim3 grid(nsplit, d.G * hgroups, d.B);
+  if (d.D == 128)
+    decode_tma_kernel<128><<<grid, DEC_THREADS, DecSmem<128>::TOTAL, c->stream>>>(mk, mv, p);
+  else
+    decode_tma_kernel<64><<<grid, DEC_THREADS, DecSmem<64>::TOTAL, c->stream>>>(mk, mv, p);
+  TB_CUDA(c, cudaGetLastError());
+  decode_combine_kernel<<<d.B * d.H, d.D, 0, c->stream>>>(p, d.D, d.P);
+  TB_CUDA(c, cudaGetLastError());
+  c->launches += 2;
+  return 0;
+}
+

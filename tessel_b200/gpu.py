@@ -189,6 +189,18 @@ class Gpu:
         e[0] += 1
         e[1] += ms.value
 
+    def decode_attention_static(self, dims: Sequence[int], q: Buf, kc: Buf, vc: Buf, table: Buf, lens: Buf, o: Buf,
+                                scale: float) -> None:
+        """Paged decode attention without any device allocation (``tb200_decode_attention_static``):
+        for hosts that handed all device memory to their own pool, or that may not allocate where
+        they run. ``dims`` = (B, H, G, D, NP, P, MP). The split-KV scratch is a 16 MiB array inside
+        the library; B*H*(D+2)*4 bytes must fit it. Make the first call on a device outside any
+        stream capture, and keep calls on one stream: they share the array."""
+        d = (C.c_int32 * 7)(*[int(x) for x in dims])
+        self.launches += 1
+        self._check(self._l.tb200_decode_attention_static(self._h, d, q.ptr, kc.ptr, vc.ptr, table.ptr, lens.ptr,
+                                                          o.ptr, scale))
+
     def profile_rows(self):
         """The profile, largest first: (phase, kernel, launches, milliseconds)."""
         rows = [(p, k, int(n), ms) for (p, k), (n, ms) in (self.profile or {}).items()]
