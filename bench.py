@@ -118,57 +118,65 @@ class Clocks:
 
 
 # ---- the CPU arm: the oracle on the host cores -----------------------------------------------
-def cpu_decode_sample(cfg, ctx, rows: int, head_div: int = 8):
-    """Times one layer and 1/head_div of the LM head of a decode step for `rows` sequences on
-    the oracle, and scales to the whole step (all layers, whole head, all sequences).
-    Returns (seconds for the sample, extrapolated seconds per full step)."""
-    import oracle
-    g = np.random.default_rng(0)
-    h = np.float16
-    dm, H, G, D, F, V = cfg.dim, cfg.heads, cfg.kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab
-    W = (H + 2 * G) * D
-    P = 16
+class CpuSample:
+    """One layer and 1/head_div of the LM head of a decode step for `rows` sequences on the
+    oracle; `run()` times it and scales to the whole step (all layers, whole head, all
+    sequences). Inputs are generated once."""
 
-    def m(r, c):
-        return (g.standard_normal((r, c), dtype=np.float32) * np.float32(0.02)).astype(h)
+    def __init__(self, cfg, ctx, rows: int, head_div: int = 8):
+        import oracle
+        self.o = oracle
+        g = np.random.default_rng(0)
+        h = np.float16
+        self.cfg, self.rows, self.head_div, self.nseq = cfg, rows, head_div, len(ctx)
+        dm, H, G, D, F, V = cfg.dim, cfg.heads, cfg.kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab
+        W = (H + 2 * G) * D
+        P = 16
 
-    wqkv, wo, wg, wu, wd = m(W, dm), m(dm, H * D), m(F, dm), m(F, dm), m(dm, F)
-    vs = V // head_div
-    head = m(vs, dm)
-    one = np.ones(dm, h)
-    lens = np.asarray(ctx[:rows], np.int32) + 1
-    pages = [-(-int(l) // P) for l in lens]
-    NP = sum(pages) + 1
-    kc = g.standard_normal((NP, P, G, D), dtype=np.float32).astype(h)
-    vc = g.standard_normal((NP, P, G, D), dtype=np.float32).astype(h)
-    MP = max(pages)
-    table = np.zeros((rows, MP), np.int32)
-    at = 0
-    for b, n in enumerate(pages):
-        table[b, :n] = np.arange(at, at + n)
-        at += n
-    x = g.standard_normal((rows, dm), dtype=np.float32)
-    pos = (lens - 1).astype(np.int32)
-    slot = np.asarray([table[b, pos[b] // P] * P + pos[b] % P for b in range(rows)], np.int32)
-    Ct, St = oracle.rope_tables(cfg.max_pos, D, cfg.rope_theta)
-    t0 = time.perf_counter()
-    hh = oracle.rmsnorm(x, one, cfg.eps)
-    qkv = oracle.linear(hh, wqkv)
-    q = oracle.rope_q(qkv, pos, Ct, St, H, D)
-    kc2, vc2, _, _ = oracle.kv_write(qkv, pos, slot, Ct, St, kc.reshape(NP * P, G, D), vc.reshape(NP * P, G, D), G, D)
-    o = oracle.decode_attention(q, kc2.reshape(NP, P, G, D), vc2.reshape(NP, P, G, D), table, lens,
-                                1.0 / math.sqrt(D))
-    x = oracle.linear_residual(o.reshape(rows, H * D), wo, x)
-    hh = oracle.rmsnorm(x, one, cfg.eps)
-    mlp = oracle.gate_up(hh, wg, wu)
-    x = oracle.linear_residual(mlp, wd, x)
-    t_layer = time.perf_counter() - t0
-    t0 = time.perf_counter()
-    last = oracle.rmsnorm_rows(x, np.arange(rows, dtype=np.int32), one, cfg.eps)
-    lg = oracle.logits(last, head)
-    [oracle.argmax(r) for r in lg]
-    t_head = time.perf_counter() - t0
-    return t_layer + t_head, (t_layer * cfg.layers + t_head * head_div) * (len(ctx) / rows)
+        def m(r, c):
+            return (g.standard_normal((r, c), dtype=np.float32) * np.float32(0.02)).astype(h)
+
+        self.wqkv, self.wo, self.wg, self.wu, self.wd = m(W, dm), m(dm, H * D), m(F, dm), m(F, dm), m(dm, F)
+        self.head = m(V // head_div, dm)
+        self.one = np.ones(dm, h)
+        self.lens = np.asarray(ctx[:rows], np.int32) + 1
+        pages = [-(-int(l) // P) for l in self.lens]
+        NP = sum(pages) + 1
+        self.kc = g.standard_normal((NP * P, G, D), dtype=np.float32).astype(h)
+        self.vc = g.standard_normal((NP * P, G, D), dtype=np.float32).astype(h)
+        self.NP, self.P = NP, P
+        self.table = np.zeros((rows, max(pages)), np.int32)
+        at = 0
+        for b, n in enumerate(pages):
+            self.table[b, :n] = np.arange(at, at + n)
+            at += n
+        self.x = g.standard_normal((rows, dm), dtype=np.float32)
+        self.pos = (self.lens - 1).astype(np.int32)
+        self.slot = np.asarray([self.table[b, self.pos[b] // P] * P + self.pos[b] % P for b in range(rows)], np.int32)
+        self.Ct, self.St = oracle.rope_tables(cfg.max_pos, D, cfg.rope_theta)
+
+    def run(self):
+        """Returns (seconds for the sample, extrapolated seconds per full step)."""
+        o, cfg, rows = self.o, self.cfg, self.rows
+        H, G, D, NP, P = cfg.heads, cfg.kv_heads, cfg.head_dim, self.NP, self.P
+        t0 = time.perf_counter()
+        hh = o.rmsnorm(self.x, self.one, cfg.eps)
+        qkv = o.linear(hh, self.wqkv)
+        q = o.rope_q(qkv, self.pos, self.Ct, self.St, H, D)
+        kc2, vc2, _, _ = o.kv_write(qkv, self.pos, self.slot, self.Ct, self.St, self.kc, self.vc, G, D)
+        att = o.decode_attention(q, kc2.reshape(NP, P, G, D), vc2.reshape(NP, P, G, D), self.table, self.lens,
+                                 1.0 / math.sqrt(D))
+        x = o.linear_residual(att.reshape(rows, H * D), self.wo, self.x)
+        hh = o.rmsnorm(x, self.one, cfg.eps)
+        mlp = o.gate_up(hh, self.wg, self.wu)
+        x = o.linear_residual(mlp, self.wd, x)
+        t_layer = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        last = o.rmsnorm_rows(x, np.arange(rows, dtype=np.int32), self.one, cfg.eps)
+        lg = o.logits(last, self.head)
+        [o.argmax(r) for r in lg]
+        t_head = time.perf_counter() - t0
+        return t_layer + t_head, (t_layer * cfg.layers + t_head * self.head_div) * (self.nseq / rows)
 
 
 def run_reference(args, wl):
@@ -182,16 +190,18 @@ def run_reference(args, wl):
     ctx = g.integers(wl["lo"], wl["hi"] + 1, seqs)
     rows = 16
     # Size the sample so that K + W steps end within a few minutes.
-    t, _ = cpu_decode_sample(cfg, ctx, rows)
+    smp = CpuSample(cfg, ctx, rows)
+    t, _ = smp.run()
     while rows > 1 and t * (args.steps + args.warmup) > 150.0:
         rows //= 2
-        t, _ = cpu_decode_sample(cfg, ctx, rows)
+        smp = CpuSample(cfg, ctx, rows)
+        t, _ = smp.run()
     for _ in range(max(0, args.warmup - 1)):
-        cpu_decode_sample(cfg, ctx, rows)
+        smp.run()
     full = []
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        full.append(cpu_decode_sample(cfg, ctx, rows)[1])
+        full.append(smp.run()[1])
     wall = time.perf_counter() - t0
     sec = statistics.mean(full)
     val = seqs / sec
@@ -400,7 +410,7 @@ def run_ours(args, wl):
     }
     if world == 1 and not args.no_cpu_baseline:
         import oracle
-        sample_s, full_s = cpu_decode_sample(cfg, [q.len for q in s.running], 16)
+        sample_s, full_s = CpuSample(cfg, [q.len for q in s.running], 16).run()
         line["cpu_baseline"] = {
             "value": n / full_s, "unit": UNIT, "cores": oracle.threads(), "kind": "port",
             "sample": (f"1 of {cfg.layers} layers and 1/8 of the LM head for 16 of {n} sequences at their current "

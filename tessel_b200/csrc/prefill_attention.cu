@@ -3,16 +3,17 @@
 //                      (kernels/llm.tl:116-145)
 //   flash_attention    Q/K/V/O [H,S,D]            (kernels/attention.tl:4-24)
 //
-// tcgen05 path (D in {64, 128}): one CTA owns 128 query rows of one head. A
-// producer warp brings the Q tile once and then 128-key K and V tiles through
-// a two-stage TMA ring. One thread issues the MMAs: S = Q K^T (M 128, N 128)
-// into tensor memory, and O_blk = P V (M 128, N D) once the softmax warps have
-// published P. Four softmax warps own one query row per thread: they read S
-// out of tensor memory, apply scale and the causal / sequence-start mask, keep
-// the online maximum and sum, round P to f16 into swizzled shared memory (the
-// A operand of the second MMA, as kernels/llm.tl:143 rounds it), then fold
-// O_blk into their f32 accumulator row. The S MMA of the next key block is
-// issued right behind the P V MMA, so it runs while the softmax warps fold.
+// tcgen05 path (D in {64, 128}): one CTA owns 256 query rows of one head as two 128-row tiles.
+// A producer warp brings both Q tiles once and then 128-key K and V tiles through a two-stage
+// TMA ring. One thread issues the MMAs: S_t = Q_t K^T (M 128, N 128) into tensor memory, and
+// O_t += P_t V (M 128, N D) with P read straight from tensor memory and O accumulated there.
+// Each tile has a softmax warpgroup, one query row per thread: it reads S out of tensor memory,
+// applies scale and the causal / sequence-start mask, rounds P to f16 (as kernels/llm.tl:143
+// does) and stores it over S's first columns. The MMA order S0 S1 | PV0 S0' | PV1 S1' | ... lets
+// one tile's softmax run while the tensor pipe works on the other tile. The running maximum is
+// lazy: O (in tensor memory) is rescaled only when a row's maximum grew by more than 2^8, which
+// leaves P <= 256 and changes no result beyond rounding; the final division by the row sum is
+// exact in the same reference maximum.
 //
 // The key loop starts at starts[first row of the block] (not tile aligned) and
 // the running maximum starts at -1e30, as the reference's does.
@@ -24,9 +25,12 @@ namespace tb {
 
 namespace {
 
-constexpr int FA_BM = 128, FA_BN = 128;
-constexpr int FA_THREADS = 192;
+constexpr int FA_BM = 128;        // query rows per tile (one MMA's M)
+constexpr int FA_TILES = 2;       // query tiles per CTA: two softmax warpgroups take turns on the tensor pipe
+constexpr int FA_BN = 128;        // keys per block
+constexpr int FA_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 and 6-9 softmax
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.0f;  // O is rescaled only when a row's maximum grew by more than 2^8
 
 struct FaParams {
   const int* starts;  // null for the plain layout
@@ -39,15 +43,16 @@ struct FaParams {
 template <int D>
 struct FaSmem {
   static constexpr int SUB = D / 64;
-  static constexpr int Q_BYTES = FA_BM * D * 2;
-  static constexpr int KV_BYTES = FA_BN * D * 2;      // one K (or V) tile
+  static constexpr int Q_TILE = FA_BM * D * 2;
+  static constexpr int Q_BYTES = FA_TILES * Q_TILE;
+  static constexpr int KV_BYTES = FA_BN * D * 2;  // one K (or V) tile
   static constexpr int STAGE = 2 * KV_BYTES;
-  static constexpr int P_BYTES = FA_BM * FA_BN * 2;
   static constexpr int OFF_KV = Q_BYTES;
-  static constexpr int OFF_P = OFF_KV + 2 * STAGE;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_BAR = OFF_KV + 2 * STAGE;
   static constexpr int TOTAL = OFF_BAR + 16 * 8 + 1024;
-  static constexpr int TMEM_COLS = 256;  // S: [0,128), O_blk: [128, 128 + D)
+  // Tensor memory: S of tile t at columns [128 t, 128 t + 128) (its first 64 columns are
+  // reused for P as packed f16 pairs), O of tile t at [256 + D t, 256 + D t + D).
+  static constexpr int TMEM_COLS = 512;
 };
 
 template <int D>
@@ -62,32 +67,36 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   uint64_t* q_full = bars + 0;
   uint64_t* kv_full = bars + 1;   // [2]
   uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;
-  uint64_t* p_full = bars + 6;
-  uint64_t* o_full = bars + 7;
-  uint64_t* o_free = bars + 8;
-  uint32_t* tmem_slot = (uint32_t*)(bars + 9);
+  uint64_t* s_full = bars + 5;    // [2], per tile
+  uint64_t* p_ready = bars + 7;   // [2]
+  uint64_t* o_done = bars + 9;    // [2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 11);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int i0 = blockIdx.x * FA_BM, h = blockIdx.y;
+  const int i0 = blockIdx.x * (FA_TILES * FA_BM), h = blockIdx.y;
   const int g = p.plain ? h : h / (p.H / p.G);
+  // Every row of the CTA starts at or after the start of its first row (prompts are packed in order).
   const int lo = p.starts ? p.starts[i0] : 0;
-  const int hi = min(i0 + FA_BM, p.S);
-  const int nblk = (hi - lo + FA_BN - 1) / FA_BN;
+  int nb[FA_TILES];
+#pragma unroll
+  for (int t = 0; t < FA_TILES; ++t) {
+    const int r0 = i0 + t * FA_BM;
+    nb[t] = r0 < p.S ? (min(r0 + FA_BM, p.S) - lo + FA_BN - 1) / FA_BN : 0;
+  }
+  const int nbmax = max(nb[0], nb[1]);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(&kv_full[0], 1);
-    mbar_init(&kv_full[1], 1);
-    mbar_init(&kv_empty[0], 1);
-    mbar_init(&kv_empty[1], 1);
-    mbar_init(s_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(o_full, 1);
-    mbar_init(o_free, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_ready[i], 128);
+      mbar_init(&o_done[i], 1);
+    }
     fence_barrier_init();
   }
-  if (warp == 5) {
+  if (warp == 1) {
     tmem_alloc(tmem_slot, SM::TMEM_COLS);
     tmem_relinquish();
   }
@@ -95,22 +104,24 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
 
-  if (warp == 4) {
+  if (warp == 0) {
     if (elect_one()) {
       prefetch_tmap(&mapQ);
       prefetch_tmap(&mapK);
       prefetch_tmap(&mapV);
       mbar_expect_tx(q_full, SM::Q_BYTES);
 #pragma unroll
-      for (int sub = 0; sub < SUB; ++sub) {
-        if (p.plain)
-          tma_load_3d(smem + sub * (FA_BM * 128), &mapQ, q_full, sub * 64, i0, h);
-        else
-          tma_load_3d(smem + sub * (FA_BM * 128), &mapQ, q_full, sub * 64, h, i0);
-      }
-      for (int jb = 0; jb < nblk; ++jb) {
+      for (int t = 0; t < FA_TILES; ++t)
+#pragma unroll
+        for (int sub = 0; sub < SUB; ++sub) {
+          unsigned char* dst = smem + t * SM::Q_TILE + sub * (FA_BM * 128);
+          if (p.plain)
+            tma_load_3d(dst, &mapQ, q_full, sub * 64, i0 + t * FA_BM, h);
+          else
+            tma_load_3d(dst, &mapQ, q_full, sub * 64, h, i0 + t * FA_BM);
+        }
+      for (int jb = 0; jb < nbmax; ++jb) {
         const int s = jb & 1, k = jb >> 1;
         const int key0 = lo + jb * FA_BN;
         mbar_wait(&kv_empty[s], (k & 1) ^ 1, p.status, 301);
@@ -129,132 +140,170 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 1) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_f16(FA_BM, FA_BN, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_f16(FA_BM, D, 0, 1);
-      const uint32_t qa = smem_u32(smem);
-      const uint32_t pa = smem_u32(smem + SM::OFF_P);
-      mbar_wait(q_full, 0, p.status, 302);
-      for (int jb = 0; jb < nblk; ++jb) {
-        const int s = jb & 1, k = jb >> 1;
-        const uint32_t ka = smem_u32(smem + SM::OFF_KV + s * SM::STAGE);
-        const uint32_t va = ka + SM::KV_BYTES;
-        mbar_wait(&kv_full[s], k & 1, p.status, 303);
-        tc_fence_after();
+      // S_t(j) = Q_t K(j)^T into tensor memory.
+      auto issue_s = [&](int t, int jb) {
+        const uint32_t qa = smem_u32(smem + t * SM::Q_TILE);
+        const uint32_t ka = smem_u32(smem + SM::OFF_KV + (jb & 1) * SM::STAGE);
 #pragma unroll
         for (int kd = 0; kd < D / 16; ++kd) {
           const uint32_t off = (kd >> 2) * (FA_BM * 128) + (kd & 3) * 32;
-          umma_f16(tmem_s, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_s,
+          umma_f16(tmem + t * 128, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_s,
                    kd > 0 ? 1u : 0u);
         }
-        umma_commit(s_full);
-        mbar_wait(p_full, jb & 1, p.status, 304);
-        if (jb > 0) mbar_wait(o_free, (jb - 1) & 1, p.status, 305);
+        umma_commit(&s_full[t]);
+      };
+      // O_t (+)= P_t V(j): P is read from tensor memory, V is an N-major operand in shared memory.
+      auto issue_pv = [&](int t, int jb) {
+        const uint32_t va = smem_u32(smem + SM::OFF_KV + (jb & 1) * SM::STAGE) + SM::KV_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < FA_BN / 16; ++kk)
+          umma_f16_ts(tmem + 256 + t * D, tmem + t * 128 + kk * 8, umma_desc_sw128(va + kk * 2048, FA_BN * 128, 1024),
+                      idesc_o, (jb > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&o_done[t]);
+      };
+      mbar_wait(q_full, 0, p.status, 302);
+      if (nbmax > 0) {
+        mbar_wait(&kv_full[0], 0, p.status, 303);
         tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < FA_BN / 16; ++kk) {
-          const uint32_t aoff = (kk >> 2) * (FA_BM * 128) + (kk & 3) * 32;
-          umma_f16(tmem_o, umma_desc_sw128(pa + aoff, 16, 1024),
-                   umma_desc_sw128(va + kk * 2048, FA_BN * 128, 1024), idesc_o, kk > 0 ? 1u : 0u);
+        for (int t = 0; t < FA_TILES; ++t)
+          if (nb[t] > 0) issue_s(t, 0);
+      }
+      for (int jb = 0; jb < nbmax; ++jb) {
+        bool next_ready = false;
+#pragma unroll
+        for (int t = 0; t < FA_TILES; ++t) {
+          if (jb < nb[t]) {
+            mbar_wait(&p_ready[t], jb & 1, p.status, 304);
+            tc_fence_after();
+            issue_pv(t, jb);
+          }
+          if (jb + 1 < nb[t]) {
+            if (!next_ready) {
+              mbar_wait(&kv_full[(jb + 1) & 1], ((jb + 1) >> 1) & 1, p.status, 305);
+              tc_fence_after();
+              next_ready = true;
+            }
+            issue_s(t, jb + 1);
+          }
         }
-        umma_commit(o_full);
-        umma_commit(&kv_empty[s]);
+        umma_commit(&kv_empty[jb & 1]);  // K(j), V(j) are free once the MMAs issued so far are done
       }
     }
   } else {
-    // ---- softmax warps: thread = query row, TMEM lanes 32*warp .. +31 -------
-    const int r = threadIdx.x;  // 0..127
-    const int row = i0 + r;
+    // ---- softmax warpgroups: thread = one query row of tile t -------------------------------
+    const int t = (warp - 2) >> 2;
+    const int q = warp & 3;  // TMEM lane quadrant this warp may touch
+    const int rit = q * 32 + lane;
+    const int row = i0 + t * FA_BM + rit;
     const int st = (p.starts && row < p.S) ? p.starts[row] : 0;
     const float sc2 = p.scale * LOG2E;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    unsigned char* prow = smem + SM::OFF_P + r * 128;
-    float m = -1e30f, l = 0.f;
-    float acc[D];
-#pragma unroll
-    for (int d = 0; d < D; ++d) acc[d] = 0.f;
-    for (int jb = 0; jb < nblk; ++jb) {
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const uint32_t tmem_s = tmem + lane_base + t * 128;
+    const uint32_t tmem_o = tmem + lane_base + 256 + t * D;
+    const int nbt = nb[t];
+    float m_ref = -1e30f, l = 0.f;
+    for (int jb = 0; jb < nbt; ++jb) {
       const int key0 = lo + jb * FA_BN;
-      mbar_wait(s_full, jb & 1, p.status, 306);
+      mbar_wait(&s_full[t], jb & 1, p.status, 306);
+      // S(j) is ordered behind P V(j-1) on the tensor pipe, so O is quiescent now.
+      if (jb > 0) mbar_wait(&o_done[t], (jb - 1) & 1, p.status, 307);
       tc_fence_after();
-      // Pass 1: the block's row maximum (log2 domain).
+      uint32_t sv[FA_BN];
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c) tmem_ld32(tmem_s + c * 32, sv + c * 32);
+      tmem_ld_wait();
+      // Scores in the log2 domain; keys beyond the diagonal, before the row's own prompt, or
+      // past the end are masked. Blocks that lie wholly inside skip the tests.
+      const bool inside = key0 + FA_BN - 1 <= row && key0 >= st && key0 + FA_BN <= p.S;
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < FA_BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s + lane_base + c0, v);
-        tmem_ld_wait();
+      if (inside) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = key0 + c0 + j;
+        for (int i = 0; i < FA_BN; ++i) {
+          const float x = __uint_as_float(sv[i]) * sc2;
+          sv[i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < FA_BN; ++i) {
+          const int col = key0 + i;
           const bool ok = col <= row && col >= st && col < p.S;
-          mx = fmaxf(mx, ok ? __uint_as_float(v[j]) * sc2 : -INFINITY);
+          const float x = ok ? __uint_as_float(sv[i]) * sc2 : -INFINITY;
+          sv[i] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
         }
       }
-      const float m2 = fmaxf(m, mx);
-      // Pass 2: probabilities, rounded to f16 into the swizzled P tile.
+      const float m_new = fmaxf(m_ref, mx);
+      // Lazy rescale: keep the old reference maximum unless this row outgrew it by 2^8.
+      const bool grow = m_new > m_ref + RESCALE_STEP;
+      if (jb == 0) {
+        m_ref = m_new;
+      } else if (__any_sync(0xffffffffu, grow)) {
+        const float f = grow ? exp2f(m_ref - m_new) : 1.0f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+          uint32_t ov[32];
+          tmem_ld32(tmem_o + c0, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+          tmem_st32(tmem_o + c0, ov);
+        }
+        tmem_st_wait();
+        l *= f;
+        if (grow) m_ref = m_new;
+      }
+      // Probabilities relative to m_ref, rounded to f16 (kernels/llm.tl:143) into tensor memory.
       float sum = 0.f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < FA_BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_s + lane_base + c0, v);
-        tmem_ld_wait();
-        float pr[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int col = key0 + c0 + j;
-          const bool ok = col <= row && col >= st && col < p.S;
-          pr[j] = ok ? exp2f(__uint_as_float(v[j]) * sc2 - m2) : 0.f;
-          sum += pr[j];
+      for (int half = 0; half < 2; ++half) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float a = exp2f(__uint_as_float(sv[half * 64 + 2 * i]) - m_ref);
+          const float b = exp2f(__uint_as_float(sv[half * 64 + 2 * i + 1]) - m_ref);
+          sum += a + b;
+          pk[i] = pack_h2(a, b);
         }
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          const int c = (c0 >> 3) + ch;  // 16-byte chunk along the keys, 0..15
-          uint4 o;
-          o.x = pack_h2(pr[ch * 8 + 0], pr[ch * 8 + 1]);
-          o.y = pack_h2(pr[ch * 8 + 2], pr[ch * 8 + 3]);
-          o.z = pack_h2(pr[ch * 8 + 4], pr[ch * 8 + 5]);
-          o.w = pack_h2(pr[ch * 8 + 6], pr[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(prow + (c >> 3) * (FA_BM * 128) + (((c & 7) ^ (r & 7)) << 4)) = o;
-        }
+        tmem_st32(tmem_s + half * 32, pk);
       }
-      const float a = exp2f(m - m2);
-      l = l * a + sum;
-      m = m2;
+      tmem_st_wait();
+      l += sum;
       tc_fence_before();
-      fence_proxy_async();  // P must be visible to the tensor core's reads
-      mbar_arrive(p_full);
-      mbar_wait(o_full, jb & 1, p.status, 307);
-      tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_o + lane_base + c0, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[c0 + j] = acc[c0 + j] * a + __uint_as_float(v[j]);
-      }
-      tc_fence_before();
-      mbar_arrive(o_free);
+      mbar_arrive(&p_ready[t]);
     }
-    if (row < p.S) {
+    if (nbt > 0) {
+      mbar_wait(&o_done[t], (nbt - 1) & 1, p.status, 308);
+      tc_fence_after();
       const float inv = 1.0f / l;
       __half* o = p.plain ? p.O + ((size_t)h * p.S + row) * D : p.O + ((size_t)row * p.H + h) * D;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        uint32_t ov[32];
+        tmem_ld32(tmem_o + c0, ov);
+        tmem_ld_wait();
+        if (row < p.S) {
 #pragma unroll
-      for (int d = 0; d < D; d += 8) {
-        uint4 w;
-        w.x = pack_h2(acc[d] * inv, acc[d + 1] * inv);
-        w.y = pack_h2(acc[d + 2] * inv, acc[d + 3] * inv);
-        w.z = pack_h2(acc[d + 4] * inv, acc[d + 5] * inv);
-        w.w = pack_h2(acc[d + 6] * inv, acc[d + 7] * inv);
-        *reinterpret_cast<uint4*>(o + d) = w;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_h2(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv);
+            w.y = pack_h2(__uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+            w.z = pack_h2(__uint_as_float(ov[i + 4]) * inv, __uint_as_float(ov[i + 5]) * inv);
+            w.w = pack_h2(__uint_as_float(ov[i + 6]) * inv, __uint_as_float(ov[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(o + c0 + i) = w;
+          }
+        }
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, SM::TMEM_COLS);
   }
@@ -357,7 +406,7 @@ int run_fa(Ctx* c, const FaShape& f, const void* Q, const void* K, const void* V
   p.G = f.G;
   p.plain = f.plain;
   p.status = c->status;
-  dim3 grid((f.S + FA_BM - 1) / FA_BM, f.H);
+  dim3 grid((f.S + FA_TILES * FA_BM - 1) / (FA_TILES * FA_BM), f.H);
   fa_kernel<D><<<grid, FA_THREADS, FaSmem<D>::TOTAL, c->stream>>>(mq, mk, mv, p);
   TB_CUDA(c, cudaGetLastError());
   return 0;
