@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   uint32_t* tmem_slot = (uint32_t*)(bars + 11);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int i0 = blockIdx.x * (FA_TILES * FA_BM), h = blockIdx.y;
+  // Late row blocks see the most keys: they are scheduled first so the grid's tail is short.
+  const int i0 = (gridDim.x - 1 - blockIdx.x) * (FA_TILES * FA_BM), h = blockIdx.y;
   const int g = p.plain ? h : h / (p.H / p.G);
   // Every row of the CTA starts at or after the start of its first row (prompts are packed in order).
   const int lo = p.starts ? p.starts[i0] : 0;
@@ -217,27 +218,25 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 #pragma unroll
       for (int c = 0; c < FA_BN / 32; ++c) tmem_ld32(tmem_s + c * 32, sv + c * 32);
       tmem_ld_wait();
-      // Scores in the log2 domain; keys beyond the diagonal, before the row's own prompt, or
-      // past the end are masked. Blocks that lie wholly inside skip the tests.
+      // Keys beyond the diagonal, before the row's own prompt, or past the end are masked.
+      // Blocks that lie wholly inside skip the tests. The scale (positive) is applied with the
+      // subtraction of the maximum, in one fused multiply-add per score.
       const bool inside = key0 + FA_BN - 1 <= row && key0 >= st && key0 + FA_BN <= p.S;
       float mx = -INFINITY;
       if (inside) {
 #pragma unroll
-        for (int i = 0; i < FA_BN; ++i) {
-          const float x = __uint_as_float(sv[i]) * sc2;
-          sv[i] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
+        for (int i = 0; i < FA_BN; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
       } else {
 #pragma unroll
         for (int i = 0; i < FA_BN; ++i) {
           const int col = key0 + i;
           const bool ok = col <= row && col >= st && col < p.S;
-          const float x = ok ? __uint_as_float(sv[i]) * sc2 : -INFINITY;
+          const float x = ok ? __uint_as_float(sv[i]) : -INFINITY;
           sv[i] = __float_as_uint(x);
           mx = fmaxf(mx, x);
         }
       }
+      mx *= sc2;  // log2 domain
       const float m_new = fmaxf(m_ref, mx);
       // Lazy rescale: keep the old reference maximum unless this row outgrew it by 2^8.
       const bool grow = m_new > m_ref + RESCALE_STEP;
@@ -265,8 +264,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         uint32_t pk[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float a = exp2f(__uint_as_float(sv[half * 64 + 2 * i]) - m_ref);
-          const float b = exp2f(__uint_as_float(sv[half * 64 + 2 * i + 1]) - m_ref);
+          const float a = exp2f(fmaf(__uint_as_float(sv[half * 64 + 2 * i]), sc2, -m_ref));
+          const float b = exp2f(fmaf(__uint_as_float(sv[half * 64 + 2 * i + 1]), sc2, -m_ref));
           sum += a + b;
           pk[i] = pack_h2(a, b);
         }
