@@ -54,6 +54,8 @@ def parse():
     ap.add_argument("--seqs", type=int, default=0, help="sequences (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile-steps", type=int, default=2)
+    ap.add_argument("--tp-exchange", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: cross-rank sums by the fused peer-memory kernel, or by NCCL allreduce")
     return ap.parse_args()
 
 
@@ -297,8 +299,14 @@ def run_ours(args, wl):
         dist.broadcast_object_list(ids, src=0)
         gpu.comm_init(rank, world, ids[0])
     w = device_weights(cfg, local, 1000 + rank, torch)
+    exchange = None
+    if world > 1 and args.tp_exchange == "fused":
+        def exchange(mine):
+            everyone = [None] * world
+            dist.all_gather_object(everyone, mine)
+            return everyone
     e = Engine(gpu, w, Limits(page=P, pages=pages, max_tokens=max_prompt, max_seq_pages=msp), rank=rank,
-               nranks=world, sharded=True)
+               nranks=world, sharded=True, exchange=exchange)
     s = Scheduler(e, reqs, seqs, packed=True, device_argmax=True)
 
     # ---- prefill (untimed for the metric; reported for information) ---------------------------
@@ -395,7 +403,7 @@ def run_ours(args, wl):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(Wm, 3),
         "ms_per_step": dev_step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": wl["label"], "sequences": n, "parallelism": f"tp{world}",
+        "config": {"workload": wl["label"], "sequences": n, "parallelism": f"tp{world}" + (f" ({args.tp_exchange} exchange)" if world > 1 else ""),
                    "l2": "inputs larger than L2 (weights + KV read per step: %.1f GB per GPU)" % (step_bytes / 1e9),
                    "mean_context": ctx_mid},
         "e2e": {"value": n * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * n,

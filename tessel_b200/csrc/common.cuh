@@ -38,6 +38,7 @@ enum Kind : int {
   K_LINEAR_F32,     // Y f32 = X W^T (a tensor-parallel rank's partial product)
   K_RESIDUAL_ADD,   // R f32 += P f32
   K_ARGMAX_ROWS,    // first index of each row's maximum
+  K_TP_REDUCE_NORM, // cross-rank sum of partial products + residual add + RMSNorm over peer memory
   K_DECODE_ADVANCE, // next decode step's tok/pos/slot/lens from this step's picks, on the device
   K_COUNT
 };
@@ -102,6 +103,13 @@ int launch_gemm(Ctx* c, Op& op, const uint64_t* a);
 int make_decode(Ctx* c, Op& op);
 int launch_decode(Ctx* c, Op& op, const uint64_t* a);
 int make_prefill(Ctx* c, Op& op);
+int make_tp(Ctx* c, Op& op);
+int launch_tp(Ctx* c, Op& op, const uint64_t* a);
+size_t tp_table_bytes();
+size_t tp_flag_bytes();
+size_t tp_epoch_bytes();
+int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint64_t* part0, const uint64_t* part1,
+                  const uint64_t* x, const uint64_t* h, const uint64_t* flags, uint64_t epoch);
 int launch_prefill(Ctx* c, Op& op, const uint64_t* a);
 
 inline float bits_f32(uint64_t v) {

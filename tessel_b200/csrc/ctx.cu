@@ -81,6 +81,7 @@ static const KindInfo KINDS[] = {
     {"residual_add", K_RESIDUAL_ADD, 2, 2},
     {"argmax_rows", K_ARGMAX_ROWS, 2, 2},
     {"decode_advance", K_DECODE_ADVANCE, 7, 10},
+    {"tp_reduce_norm", K_TP_REDUCE_NORM, 3, 7},
 };
 
 static bool is_gemm(Kind k) {
@@ -298,6 +299,8 @@ int tb200_kernel(tb200_ctx* h, const char* name, const int64_t* shapes, const in
     r = make_decode(c, op);
   else if (op.kind == K_PREFILL_ATTENTION || op.kind == K_FLASH_ATTENTION)
     r = make_prefill(c, op);
+  else if (op.kind == K_TP_REDUCE_NORM)
+    r = make_tp(c, op);
   else
     r = make_glue(c, op);
   if (r) return r;
@@ -324,6 +327,8 @@ int tb200_launch(tb200_ctx* h, tb200_op id, const uint64_t* args, int n_args) {
     r = launch_decode(c, op, args);
   else if (op.kind == K_PREFILL_ATTENTION || op.kind == K_FLASH_ATTENTION)
     r = launch_prefill(c, op, args);
+  else if (op.kind == K_TP_REDUCE_NORM)
+    r = launch_tp(c, op, args);
   else
     r = launch_glue(c, op, args);
   return r;
@@ -483,6 +488,41 @@ int tb200_allreduce(tb200_ctx* h, uint64_t dptr, size_t count, int dtype) {
   int r = f((const void*)dptr, (void*)dptr, count, dtype == 0 ? nccl_f32 : nccl_f16, nccl_sum, c->comm, c->stream);
   if (r) return nccl_fail(c, r, "ncclAllReduce");
   c->launches += 1;
+  return 0;
+}
+
+int tb200_ipc_export(tb200_ctx* h, uint64_t dptr, void* handle) {
+  Ctx* c = &h->c;
+  static_assert(sizeof(cudaIpcMemHandle_t) == TB200_IPC_HANDLE_BYTES, "IPC handle size");
+  TB_CUDA(c, cudaSetDevice(c->device));
+  TB_CUDA(c, cudaIpcGetMemHandle((cudaIpcMemHandle_t*)handle, (void*)dptr));
+  return 0;
+}
+
+int tb200_ipc_import(tb200_ctx* h, const void* handle, uint64_t* dptr) {
+  Ctx* c = &h->c;
+  TB_CUDA(c, cudaSetDevice(c->device));
+  cudaIpcMemHandle_t hd;
+  memcpy(&hd, handle, sizeof hd);
+  void* p = nullptr;
+  TB_CUDA(c, cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess));
+  *dptr = (uint64_t)p;
+  return 0;
+}
+
+int tb200_tp_sizes(size_t* table_bytes, size_t* flag_bytes, size_t* epoch_bytes) {
+  if (table_bytes) *table_bytes = tp_table_bytes();
+  if (flag_bytes) *flag_bytes = tp_flag_bytes();
+  if (epoch_bytes) *epoch_bytes = tp_epoch_bytes();
+  return 0;
+}
+
+int tb200_tp_table(tb200_ctx* h, void* out, size_t bytes, int rank, int nranks, const uint64_t* part0,
+                   const uint64_t* part1, const uint64_t* x, const uint64_t* hh, const uint64_t* flags,
+                   uint64_t epoch) {
+  Ctx* c = &h->c;
+  if (tp_fill_table(out, bytes, rank, nranks, part0, part1, x, hh, flags, epoch))
+    return fail(c, "tb200_tp_table: 1 to 8 ranks, rank inside, and a buffer of tb200_tp_sizes' table size");
   return 0;
 }
 

@@ -1,0 +1,228 @@
+// Tensor-parallel exchange fused with the residual add and the next RMSNorm.
+//
+// Under tensor parallelism o_proj and down_proj leave, on every rank, an f32 partial product
+// part[T, dim] whose sum over ranks must be added to the residual stream x (replicated on every
+// rank) and then normalised into h for the next projection. The plain path does that with four
+// launches: linear_f32, an NCCL allreduce, residual_add, rmsnorm. `tp_reduce_norm` does the last
+// three in ONE kernel over peer memory (buffers of the other ranks mapped through CUDA IPC and
+// reached over NVLink with ordinary loads and stores; no multicast, no TMA):
+//
+//   1. every CTA tells the same-numbered CTA of every peer that this rank's partial is
+//      complete (the kernel runs behind the rank's GEMM on the same stream) and waits for theirs;
+//   2. the row r of the step belongs to rank r % n: its owner loads that row of all n partials
+//      (peers' over NVLink), adds them in rank order to its x row, normalises, and stores the
+//      new x row and h row into EVERY rank's x and h (reduce-scatter and all-gather in one pass,
+//      so each value crosses NVLink once in and once out);
+//   3. every CTA tells its peers that its rows are out, and waits for theirs, so that when the
+//      kernel ends on a rank all of that rank's x and h rows have arrived.
+//
+// Sums are taken in rank order by one owner, so x and h are bit-identical on all ranks, which
+// keeps the replicated LM heads (and the greedy tokens) in lockstep. Flag waits are bounded:
+// on time-out the kernel raises the context's status word and returns.
+#include "common.cuh"
+
+namespace tb {
+
+namespace {
+
+constexpr int TP_MAX = 8;
+constexpr int TP_SLOTS = 4096;  // CTAs a launch may have (rows of the largest step / ranks)
+constexpr int TP_THREADS = 1024;
+
+// Lives in device memory; written once by the host after the ranks exchanged IPC handles.
+struct TpTable {
+  float* part[2][TP_MAX];   // the two partial-product buffers of every rank
+  float* x[TP_MAX];         // residual stream of every rank
+  __half* h[TP_MAX];        // normalised activations of every rank
+  unsigned int* flags[TP_MAX];  // [TP_SLOTS][2 phases][TP_MAX senders]
+  unsigned int* epoch;      // [TP_SLOTS], local: launches this slot has taken part in
+  int rank, nranks;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Thread `tid` < nranks signals peer `tid` and waits for peer `tid`'s signal of this epoch.
+__device__ __forceinline__ void exchange_flags(const TpTable& tb_, int slot, int phase, unsigned int epoch,
+                                               unsigned int* status, unsigned int code) {
+  const int tid = threadIdx.x;
+  if (tid < tb_.nranks && tid != tb_.rank) {
+    st_release_sys(tb_.flags[tid] + ((size_t)slot * 2 + phase) * TP_MAX + tb_.rank, epoch);
+    const unsigned int* mine = tb_.flags[tb_.rank] + ((size_t)slot * 2 + phase) * TP_MAX + tid;
+    const unsigned long long t0 = globaltimer();
+    unsigned int spins = 0;
+    // Epochs only grow; a peer that is a launch ahead has already passed this one.
+    while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 255u) == 0) {
+        if (*(volatile unsigned int*)status != 0) break;
+        if (globaltimer() - t0 > WAIT_LIMIT_NS / 2) {
+          atomicCAS(status, 0u, code);
+          break;
+        }
+      }
+    }
+  }
+}
+
+template <int PER>  // float4 chunks per thread: dim <= PER * 4096
+__global__ void __launch_bounds__(TP_THREADS, 1)
+    tp_reduce_norm_kernel(const TpTable* __restrict__ table, const __half* __restrict__ W, float eps, int T, int dim,
+                          int which, int do_norm, unsigned int* status) {
+  __shared__ TpTable tb_;
+  __shared__ float red[32];
+  __shared__ unsigned int s_epoch;
+  if (threadIdx.x == 0) {
+    tb_ = *table;
+    s_epoch = tb_.epoch[blockIdx.x] + 1;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  const int n = tb_.nranks, rank = tb_.rank;
+  __threadfence_system();
+  exchange_flags(tb_, blockIdx.x, 0, epoch, status, 401);
+  __syncthreads();
+
+  for (int row = blockIdx.x * n + rank; row < T; row += gridDim.x * n) {
+    float4 acc[PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int c = (threadIdx.x + i * TP_THREADS) * 4;
+      if (c < dim) {
+        const size_t o = (size_t)row * dim + c;
+        float4 part[TP_MAX];
+#pragma unroll
+        for (int r = 0; r < TP_MAX; ++r)
+          if (r < n) part[r] = *reinterpret_cast<const float4*>(tb_.part[which][r] + o);
+        float4 s = part[0];
+#pragma unroll
+        for (int r = 1; r < TP_MAX; ++r)
+          if (r < n) {
+            s.x = __fadd_rn(s.x, part[r].x);
+            s.y = __fadd_rn(s.y, part[r].y);
+            s.z = __fadd_rn(s.z, part[r].z);
+            s.w = __fadd_rn(s.w, part[r].w);
+          }
+        float4 x = *reinterpret_cast<const float4*>(tb_.x[rank] + o);
+        x.x = __fadd_rn(x.x, s.x);
+        x.y = __fadd_rn(x.y, s.y);
+        x.z = __fadd_rn(x.z, s.z);
+        x.w = __fadd_rn(x.w, s.w);
+        acc[i] = x;
+#pragma unroll
+        for (int r = 0; r < TP_MAX; ++r)
+          if (r < n) *reinterpret_cast<float4*>(tb_.x[r] + o) = x;
+        ss += __fmul_rn(x.x, x.x);
+        ss += __fmul_rn(x.y, x.y);
+        ss += __fmul_rn(x.z, x.z);
+        ss += __fmul_rn(x.w, x.w);
+      }
+    }
+    if (do_norm) {
+      // Block sum of squares (kernels/llm.tl:23), then x * rsqrt(ms + eps) * w.
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float tot = red[threadIdx.x & 31];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      __syncthreads();
+      const float ms = __fdiv_rn(tot, (float)dim);
+      const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, eps)));
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int c = (threadIdx.x + i * TP_THREADS) * 4;
+        if (c < dim) {
+          const __half2 w01 = *reinterpret_cast<const __half2*>(W + c);
+          const __half2 w23 = *reinterpret_cast<const __half2*>(W + c + 2);
+          uint2 y;
+          y.x = pack_h2(__fmul_rn(__fmul_rn(acc[i].x, rs), __low2float(w01)),
+                        __fmul_rn(__fmul_rn(acc[i].y, rs), __high2float(w01)));
+          y.y = pack_h2(__fmul_rn(__fmul_rn(acc[i].z, rs), __low2float(w23)),
+                        __fmul_rn(__fmul_rn(acc[i].w, rs), __high2float(w23)));
+          const size_t o = (size_t)row * dim + c;
+#pragma unroll
+          for (int r = 0; r < TP_MAX; ++r)
+            if (r < n) *reinterpret_cast<uint2*>(tb_.h[r] + o) = y;
+        }
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  exchange_flags(tb_, blockIdx.x, 1, epoch, status, 402);
+  __syncthreads();
+  if (threadIdx.x == 0) tb_.epoch[blockIdx.x] = epoch;
+}
+
+}  // namespace
+
+// Shapes: table u8[bytes], W f16[dim], X f32[T, dim]. Arguments: table, W, X (this rank's own
+// residual stream; it must be the buffer the table names), eps, which (0/1: the partial buffer
+// this projection wrote), do_norm, nranks (the table's).
+int make_tp(Ctx* c, Op& op) {
+  const auto& s = op.shapes;
+  if (s[0].size() != 1 || s[1].size() != 1 || s[2].size() != 2 || s[1][0] != s[2][1])
+    return fail(c, op.name + ": shapes are table[bytes], W[dim], X[T, dim]");
+  if ((size_t)s[0][0] < sizeof(TpTable)) return fail(c, op.name + ": the table is too small");
+  const int64_t dim = s[2][1];
+  if (dim % 4 || dim > 2 * 4 * TP_THREADS) return fail(c, op.name + ": dim must be a multiple of 4, at most 8192");
+  return 0;
+}
+
+int launch_tp(Ctx* c, Op& op, const uint64_t* a) {
+  const auto& s = op.shapes;
+  const int T = (int)s[2][0], dim = (int)s[2][1];
+  if (T == 0) return 0;
+  const float eps = bits_f32(a[3]);
+  const int which = (int)(uint32_t)a[4], do_norm = (int)(uint32_t)a[5];
+  if (which < 0 || which > 1) return fail(c, op.name + ": which is 0 or 1");
+  if (c->nranks < 2) return fail(c, op.name + ": needs tb200_comm_init with at least two ranks");
+  // One CTA per row this rank owns; every rank launches the same grid.
+  // At most one CTA per SM, so that the CTAs that wait on each other across ranks are all resident.
+  int grid = (T + c->nranks - 1) / c->nranks;
+  if (grid > c->sm_count) grid = c->sm_count;
+  if (grid > TP_SLOTS) grid = TP_SLOTS;
+  if (dim <= 4 * TP_THREADS)
+    tp_reduce_norm_kernel<1><<<grid, TP_THREADS, 0, c->stream>>>((const TpTable*)a[0], (const __half*)a[1], eps, T,
+                                                                 dim, which, do_norm, c->status);
+  else
+    tp_reduce_norm_kernel<2><<<grid, TP_THREADS, 0, c->stream>>>((const TpTable*)a[0], (const __half*)a[1], eps, T,
+                                                                 dim, which, do_norm, c->status);
+  TB_CUDA(c, cudaGetLastError());
+  c->launches += 1;
+  return 0;
+}
+
+size_t tp_table_bytes() { return sizeof(TpTable); }
+size_t tp_flag_bytes() { return (size_t)TP_SLOTS * 2 * TP_MAX * sizeof(unsigned int); }
+size_t tp_epoch_bytes() { return (size_t)TP_SLOTS * sizeof(unsigned int); }
+
+// Fills a host copy of the table. Pointer arrays are indexed by rank.
+int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint64_t* part0, const uint64_t* part1,
+                  const uint64_t* x, const uint64_t* h, const uint64_t* flags, uint64_t epoch) {
+  if (out_bytes < sizeof(TpTable) || nranks < 1 || nranks > TP_MAX || rank < 0 || rank >= nranks) return 1;
+  TpTable t;
+  memset(&t, 0, sizeof t);
+  for (int r = 0; r < nranks; ++r) {
+    t.part[0][r] = (float*)part0[r];
+    t.part[1][r] = (float*)part1[r];
+    t.x[r] = (float*)x[r];
+    t.h[r] = (__half*)h[r];
+    t.flags[r] = (unsigned int*)flags[r];
+  }
+  t.epoch = (unsigned int*)epoch;
+  t.rank = rank;
+  t.nranks = nranks;
+  memcpy(out, &t, sizeof t);
+  return 0;
+}
+
+}  // namespace tb

@@ -105,8 +105,14 @@ class _DevLayer:
 class Engine:
     """``w`` holds the full model; with ``nranks > 1`` this engine keeps rank ``rank``'s shard of it."""
 
-    def __init__(self, gpu: Gpu, w: Weights, lim: Limits, rank: int = 0, nranks: int = 1, sharded: bool = False):
-        """``sharded``: ``w`` already is this rank's shard (its ``cfg`` the local shape)."""
+    def __init__(self, gpu: Gpu, w: Weights, lim: Limits, rank: int = 0, nranks: int = 1, sharded: bool = False,
+                 exchange=None):
+        """``sharded``: ``w`` already is this rank's shard (its ``cfg`` the local shape).
+        ``exchange``: with ``nranks > 1``, a function that takes this rank's list of byte strings and
+        returns every rank's list (an all-gather on the host). When given, the ranks map each
+        other's buffers and the cross-rank sum after o_proj and down_proj runs fused with the
+        residual add and the next RMSNorm in one kernel over NVLink (``tp_reduce_norm``) instead
+        of linear_f32 -> NCCL allreduce -> residual_add -> rmsnorm."""
         full = w.cfg
         if full.heads % full.kv_heads or full.head_dim % 2:
             raise ValueError("heads must be a multiple of kv_heads, head_dim even")
@@ -159,6 +165,19 @@ class Engine:
         self._logits_host: Optional[np.ndarray] = None
         self._hist: Optional[Buf] = None
         self._hist_rows = 0
+        self.tp_table: Optional[Buf] = None
+        if nranks > 1 and exchange is not None:
+            _, fb, eb = gpu.tp_sizes()
+            self.part2 = a(t * cfg.dim * 4)
+            self.tp_flags, self.tp_epoch = a(fb), a(eb)
+            mine = [self.part, self.part2, self.x, self.h, self.tp_flags]
+            everyone = exchange([gpu.ipc_export(b) for b in mine])
+            cols = [[], [], [], [], []]
+            for r in range(nranks):
+                for i, b in enumerate(mine):
+                    cols[i].append(b if r == rank else gpu.ipc_import(everyone[r][i], b.bytes))
+            raw = gpu.tp_table(rank, nranks, cols[0], cols[1], cols[2], cols[3], cols[4], self.tp_epoch)
+            self.tp_table = gpu.tensor(np.frombuffer(raw, np.uint8).copy())
 
     # -- one step ----------------------------------------------------------------
     def _upload(self, tokens, pos, slots, attn, want):
@@ -329,6 +348,10 @@ class Engine:
             g.launch(radd, [self.x, self.part])
 
         g.launch(embed, [self.tok, self.embed, self.x])
+        if self.tp_table is not None:
+            self._launch_layers_fused(t, prefill, norm, qkv, rope, kvw, att, oproj, gu, down, eps, scale)
+            self._launch_head(t, bw, greedy, eps)
+            return
         for l in self.layers:
             g.launch(norm, [self.x, l.n1, self.h, eps])
             g.launch(qkv, [self.h, l.wqkv, self.qkv])
@@ -342,6 +365,35 @@ class Engine:
             g.launch(norm, [self.x, l.n2, self.h, eps])
             g.launch(gu, [self.h, l.wg, l.wu, self.mlp])
             project(down, self.mlp, l.wd)
+        self._launch_head(t, bw, greedy, eps)
+
+    def _launch_layers_fused(self, t, prefill, norm, qkv, rope, kvw, att, oproj, gu, down, eps, scale) -> None:
+        """The decoder layers under tensor parallelism with the fused cross-rank reduction: each
+        projection pair ends in one ``tp_reduce_norm`` that sums the ranks' partials into the
+        residual stream and writes the next layer input h on every rank."""
+        from .gpu import I32
+        g, dm = self.gpu, self.cfg.dim
+        tpk = g.kernel("tp_reduce_norm", [[self.tp_table.bytes], [dm], [t, dm]])
+        g.launch(norm, [self.x, self.layers[0].n1, self.h, eps])
+        for i, l in enumerate(self.layers):
+            g.launch(qkv, [self.h, l.wqkv, self.qkv])
+            g.launch(rope, [self.qkv, self.pos, self.cos, self.sin, self.q])
+            g.launch(kvw, [self.qkv, self.pos, self.slot, self.cos, self.sin, l.kc, l.vc, self.k, self.v])
+            if prefill:
+                g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
+            else:
+                g.launch(att, [self.q, l.kc, l.vc, self.table, self.lens, self.o, scale])
+            g.launch(oproj, [self.o, l.wo, self.part])
+            g.launch(tpk, [self.tp_table, l.n2, self.x, eps, I32(0), I32(1), I32(self.nranks)])
+            g.launch(gu, [self.h, l.wg, l.wu, self.mlp])
+            g.launch(down, [self.mlp, l.wd, self.part2])
+            last = i + 1 == len(self.layers)
+            nxt = l.n2 if last else self.layers[i + 1].n1
+            g.launch(tpk, [self.tp_table, nxt, self.x, eps, I32(1), I32(0 if last else 1), I32(self.nranks)])
+
+    def _launch_head(self, t: int, bw: Optional[int], greedy: bool, eps) -> None:
+        cfg, g, k = self.cfg, self.gpu, self.gpu.kernel
+        dm, v = cfg.dim, cfg.vocab
         if bw is None:
             return
         fin = k("rmsnorm_rows", [[t, dm], [bw], [dm], [bw, dm]])

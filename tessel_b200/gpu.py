@@ -250,5 +250,30 @@ class Gpu:
         buf = C.create_string_buffer(comm_id, _lib.COMM_ID_BYTES)
         self._check(self._l.tb200_comm_init(self._h, rank, nranks, buf))
 
+    def ipc_export(self, b: Buf) -> bytes:
+        buf = C.create_string_buffer(64)
+        self._check(self._l.tb200_ipc_export(self._h, b.ptr, buf))
+        return buf.raw
+
+    def ipc_import(self, handle: bytes, nbytes: int) -> Buf:
+        p = C.c_uint64()
+        self._check(self._l.tb200_ipc_import(self._h, C.create_string_buffer(handle, 64), C.byref(p)))
+        return Buf(p.value, nbytes)
+
+    def tp_sizes(self):
+        """(table, flags, epochs) byte sizes of the fused cross-rank reduction's bookkeeping."""
+        a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        self._check(self._l.tb200_tp_sizes(C.byref(a), C.byref(b), C.byref(c)))
+        return a.value, b.value, c.value
+
+    def tp_table(self, rank: int, nranks: int, part0, part1, x, h, flags, epoch: Buf) -> bytes:
+        """The table ``tp_reduce_norm`` reads: lists of Buf indexed by rank."""
+        n = self.tp_sizes()[0]
+        out = C.create_string_buffer(n)
+        arr = lambda bs: (C.c_uint64 * 8)(*[b.ptr for b in bs])
+        self._check(self._l.tb200_tp_table(self._h, out, n, rank, nranks, arr(part0), arr(part1), arr(x), arr(h),
+                                           arr(flags), epoch.ptr))
+        return out.raw
+
     def allreduce(self, b: Buf, count: int, dtype: int = 0) -> None:
         self._check(self._l.tb200_allreduce(self._h, b.ptr, count, dtype))

@@ -77,3 +77,6 @@ def test_two_ranks_on_gpus(tmp_path):
     one = launch("gpu", 1, str(tmp_path))
     two = launch("gpu", 2, str(tmp_path))
     compare(one, two, 2e-3)
+    # The same with the sum, the residual add and the RMSNorm fused into one kernel over NVLink.
+    fused = launch("gpufused", 2, str(tmp_path))
+    compare(one, fused, 2e-3)

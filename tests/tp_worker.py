@@ -1,9 +1,10 @@
 """One rank of a tensor-parallel engine run (launched by the tests, 2 ranks).
 
-    python tests/tp_worker.py cpu|gpu <rank> <world> <port> <out.npz>
+    python tests/tp_worker.py cpu|gpu|gpufused <rank> <world> <port> <out.npz>
 
 cpu: the engine on the oracle stand-in, the allreduce over gloo. gpu: the engine on the
-library, the allreduce over NCCL (NVLS off, plain peer transport). Rank 0 writes the prefill
+library, the allreduce over NCCL (NVLS off, plain peer transport). gpufused: the cross-rank sum
+fused with residual add and RMSNorm over peer memory (tp_reduce_norm). Rank 0 writes the prefill
 logits, one decode step's logits, the greedy tokens of a short generation and its KV cache
 shard; the other ranks write their cache shards.
 """
@@ -30,13 +31,13 @@ def requests(cfg):
     return [Request(g.integers(0, cfg.vocab, n).tolist(), 12) for n in (40, 7, 33)]
 
 
-def run(gpu, rank, world, out):
+def run(gpu, rank, world, out, exchange=None):
     from tessel_b200.engine import Decode, Engine, Limits, Packed
     from tessel_b200.model import argmax
     from tessel_b200.sched import generate_with
     cfg, w = model()
     lim = Limits(page=16, pages=40, max_tokens=128, max_seq_pages=8)
-    e = Engine(gpu, w, lim, rank=rank, nranks=world)
+    e = Engine(gpu, w, lim, rank=rank, nranks=world, exchange=exchange)
     g = np.random.default_rng(1)
     p1, p2 = g.integers(0, cfg.vocab, 37).tolist(), g.integers(0, cfg.vocab, 20).tolist()
     toks, pos = p1 + p2, list(range(37)) + list(range(20))
@@ -45,7 +46,8 @@ def run(gpu, rank, world, out):
     t1, t2 = argmax(pre[0]), argmax(pre[1])
     dec = e.step([t1, t2], [37, 20], [16 * 5 + 5, 16 * 10 + 4], Decode([[3, 4, 5], [9, 10]], [38, 21]), [0, 1]).copy()
     kc, vc = e.read_cache(1)
-    e2 = Engine(gpu, w, Limits(page=16, pages=64, max_tokens=128, max_seq_pages=8), rank=rank, nranks=world)
+    e2 = Engine(gpu, w, Limits(page=16, pages=64, max_tokens=128, max_seq_pages=8), rank=rank, nranks=world,
+                exchange=exchange)
     outs, _ = generate_with(e2, requests(cfg), 3, True, device_argmax=True)
     np.savez(out, pre=pre, dec=dec, kc=kc, vc=vc, tokens=np.asarray([o.tokens for o in outs]))
 
@@ -74,7 +76,13 @@ def main():
             ids = [gpu.comm_id() if rank == 0 else None]
             dist.broadcast_object_list(ids, src=0)
             gpu.comm_init(rank, world, ids[0])
-    run(gpu, rank, world, out)
+    exchange = None
+    if mode == "gpufused" and world > 1:
+        def exchange(mine):
+            everyone = [None] * world
+            dist.all_gather_object(everyone, mine)
+            return everyone
+    run(gpu, rank, world, out, exchange)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
