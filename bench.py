@@ -53,6 +53,7 @@ def parse():
     ap.add_argument("--workload", default="llama3-8b", choices=["llama3-8b", "tinyllama"])
     ap.add_argument("--seqs", type=int, default=0, help="sequences (default: the workload's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-micro", action="store_true", help="skip the single-kernel numbers (N = 1)")
     ap.add_argument("--profile-steps", type=int, default=2)
     ap.add_argument("--tp-exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: cross-rank sums by the fused peer-memory kernel, or by NCCL allreduce")
@@ -416,6 +417,22 @@ def run_ours(args, wl):
         "prefill": {"seconds": prefill_s, "prompt_tokens": int(s.st.prompt_tokens),
                     "tok_s": s.st.prompt_tokens / prefill_s, "steps": s.st.prefill_steps},
     }
+    if world == 1 and not args.no_micro:
+        # The two other headline numbers of the path (and the prefill attention), same process:
+        # single kernels at BASELINE configs' shapes, CUDA events per launch, L2 flushed in between.
+        from tessel_b200 import microbench as mb
+        d = mb.decode(gpu, torch, iters=10)
+        gm = mb.gemm(gpu, torch, 4096, 4096, 4096, "matmul", iters=10)
+        fl = mb.flash(gpu, torch, 256, 4096, 128, iters=5)
+        gpu.set_stream(None)
+        line["micro"] = {
+            "paged_decode_attention": {"gbs": d["gbs"], "frac_of_hbm_peak": d["frac"], "ms": d["ms"],
+                                       "shape": "256 seqs, ctx U[512,2304], 32 heads / 8 kv heads, D 128, page 16"},
+            "gemm_4096": {"tflops": gm["tflops"], "frac_of_tensor_peak": gm["frac_tensor"], "ms": gm["ms"],
+                          "shape": "f16 4096^3, row-major A and B, f32 accumulate"},
+            "flash_attention": {"tflops": fl["tflops"], "frac_of_tensor_peak": fl["frac_tensor"], "ms": fl["ms"],
+                                "shape": "causal, batch 8 x 32 heads, S 4096, D 128"},
+            "peak_kind": pk["kind"]}
     if world == 1 and not args.no_cpu_baseline:
         import oracle
         sample_s, full_s = CpuSample(cfg, [q.len for q in s.running], 16).run()
