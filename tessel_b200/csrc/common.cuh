@@ -78,15 +78,19 @@ struct Ctx {
   void* nccl_lib = nullptr;
   void* comm = nullptr;
   int rank = 0, nranks = 1;
+  // Launch every kernel with programmatic dependent launch: the next kernel's blocks may become
+  // resident (and run their set-up) while this one drains; each kernel waits for its
+  // predecessor itself (griddepcontrol.wait) before it touches activations. TB200_PDL=0 turns it off.
+  bool pdl = true;
 };
 
 int fail(Ctx* c, const std::string& msg);
 int cuda_fail(Ctx* c, cudaError_t e, const char* what);
 
-#define TB_CUDA(c, expr)                                      \
-  do {                                                        \
-    cudaError_t e__ = (expr);                                 \
-    if (e__ != cudaSuccess) return cuda_fail((c), e__, #expr); \
+#define TB_CUDA(c, ...)                                              \
+  do {                                                               \
+    cudaError_t e__ = (__VA_ARGS__);                                 \
+    if (e__ != cudaSuccess) return cuda_fail((c), e__, #__VA_ARGS__); \
   } while (0)
 
 // A tiled tensor map over a row-major array of `rank` dims (dims[0] innermost).
@@ -112,6 +116,34 @@ int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint6
                   const uint64_t* x, const uint64_t* h, const uint64_t* flags, uint64_t epoch);
 int launch_prefill(Ctx* c, Op& op, const uint64_t* a);
 
+// Launches `kern` on the context's stream, as a cluster of (1, 1, cluster_z) when cluster_z > 1.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_k(Ctx* c, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_z,
+                            Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = c->stream;
+  cudaLaunchAttribute at[2];
+  int n = 0;
+  if (cluster_z > 1) {
+    at[n].id = cudaLaunchAttributeClusterDimension;
+    at[n].val.clusterDim.x = 1;
+    at[n].val.clusterDim.y = 1;
+    at[n].val.clusterDim.z = (unsigned)cluster_z;
+    ++n;
+  }
+  if (c->pdl) {
+    at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = at;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 inline float bits_f32(uint64_t v) {
   uint32_t u = (uint32_t)v;
   float f;
@@ -127,6 +159,12 @@ inline float bits_f32(uint64_t v) {
 // Waits give up after this many nanoseconds, raise the status word and let the
 // kernel run to its end (results are then garbage, the context stays usable).
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+// Programmatic dependent launch. pdl_launch: the next kernel in the stream may start being
+// scheduled. pdl_wait: everything the previous kernels wrote is complete and visible; every
+// thread calls it before it reads or writes a buffer another kernel touches.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

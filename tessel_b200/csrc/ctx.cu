@@ -121,6 +121,7 @@ int tb200_init(int device, tb200_ctx** out) {
   Ctx* c = &h->c;
   c->device = device;
   c->sm_count = p.multiProcessorCount;
+  if (const char* e = getenv("TB200_PDL")) c->pdl = atoi(e) != 0;
   auto bail = [&](cudaError_t er, const char* what) {
     cuda_fail(nullptr, er, what);
     delete h;

@@ -82,6 +82,8 @@ template <int D>
 __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_constant__ CUtensorMap mapK,
                                                                  const __grid_constant__ CUtensorMap mapV,
                                                                  const DecodeParams p) {
+  pdl_launch();
+  pdl_wait();
   using SM = DecSmem<D>;
   constexpr int SUB = SM::SUB;
   constexpr int P = 16;
@@ -275,6 +277,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
 // A sequence with lens == 0 has no partial and gives 0/0 = NaN, as the
 // reference does (kernels/llm.tl:172 with l == 0).
 __global__ void decode_combine_kernel(const DecodeParams p, int D, int P) {
+  pdl_launch();
+  pdl_wait();
   const int bh = blockIdx.x;
   const int b = bh / p.H;
   const int n = p.lens[b];
@@ -299,6 +303,8 @@ __global__ void decode_generic_kernel(const __half* __restrict__ Q, const __half
                                       const __half* __restrict__ Vc, const int* __restrict__ table,
                                       const int* __restrict__ lens, __half* __restrict__ O, float scale, int B, int H,
                                       int G, int D, int NP, int P, int MP) {
+  pdl_launch();
+  pdl_wait();
   const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (w >= B * H) return;
   const int b = w / H, h = w % H, g = h / (H / G);
@@ -400,9 +406,9 @@ int launch_decode(Ctx* c, Op& op, const uint64_t* a) {
   const float scale = bits_f32(a[6]);
   if (!op.p0) {
     const int warps = d.B * d.H;
-    decode_generic_kernel<<<(warps + 3) / 4, 128, 0, c->stream>>>(
+    TB_CUDA(c, launch_k(c, decode_generic_kernel, dim3((warps + 3) / 4), dim3(128), 0, 1, 
         (const __half*)a[0], (const __half*)a[1], (const __half*)a[2], (const int*)a[3], (const int*)a[4],
-        (__half*)a[5], scale, d.B, d.H, d.G, d.D, d.NP, d.P, d.MP);
+        (__half*)a[5], scale, d.B, d.H, d.G, d.D, d.NP, d.P, d.MP));
     c->launches += 1;
     TB_CUDA(c, cudaGetLastError());
     return 0;
@@ -438,11 +444,11 @@ int launch_decode(Ctx* c, Op& op, const uint64_t* a) {
   const int hgroups = (d.H / d.G + 7) / 8;
   dim3 grid(p.nsplit, d.G * hgroups, d.B);
   if (d.D == 128)
-    decode_tma_kernel<128><<<grid, DEC_THREADS, DecSmem<128>::TOTAL, c->stream>>>(mk, mv, p);
+    TB_CUDA(c, launch_k(c, decode_tma_kernel<128>, dim3(grid), dim3(DEC_THREADS), DecSmem<128>::TOTAL, 1, mk, mv, p));
   else
-    decode_tma_kernel<64><<<grid, DEC_THREADS, DecSmem<64>::TOTAL, c->stream>>>(mk, mv, p);
+    TB_CUDA(c, launch_k(c, decode_tma_kernel<64>, dim3(grid), dim3(DEC_THREADS), DecSmem<64>::TOTAL, 1, mk, mv, p));
   TB_CUDA(c, cudaGetLastError());
-  decode_combine_kernel<<<d.B * d.H, d.D, 0, c->stream>>>(p, d.D, d.P);
+  TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3(d.B * d.H), dim3(d.D), 0, 1, p, d.D, d.P));
   TB_CUDA(c, cudaGetLastError());
   c->launches += 2;
   return 0;
@@ -492,10 +498,10 @@ extern "C" int tb200_decode_attention_static(tb200_ctx* h, const int32_t* dims, 
   if (!fast) {
     // The one-warp-per-head kernel keeps everything in registers: it has no scratch at all.
     const int warps = d.B * d.H;
-    decode_generic_kernel<<<(warps + 3) / 4, 128, 0, c->stream>>>((const __half*)q, (const __half*)kc,
+    TB_CUDA(c, launch_k(c, decode_generic_kernel, dim3((warps + 3) / 4), dim3(128), 0, 1, (const __half*)q, (const __half*)kc,
                                                                   (const __half*)vc, (const int*)table,
                                                                   (const int*)lens, (__half*)o, scale, d.B, d.H, d.G,
-                                                                  d.D, d.NP, d.P, d.MP);
+                                                                  d.D, d.NP, d.P, d.MP));
     TB_CUDA(c, cudaGetLastError());
     c->launches += 1;
     return 0;
@@ -561,11 +567,11 @@ extern "C" int tb200_decode_attention_static(tb200_ctx* h, const int32_t* dims, 
   p.status = c->status;
   dim3 grid(nsplit, d.G * hgroups, d.B);
   if (d.D == 128)
-    decode_tma_kernel<128><<<grid, DEC_THREADS, DecSmem<128>::TOTAL, c->stream>>>(mk, mv, p);
+    TB_CUDA(c, launch_k(c, decode_tma_kernel<128>, dim3(grid), dim3(DEC_THREADS), DecSmem<128>::TOTAL, 1, mk, mv, p));
   else
-    decode_tma_kernel<64><<<grid, DEC_THREADS, DecSmem<64>::TOTAL, c->stream>>>(mk, mv, p);
+    TB_CUDA(c, launch_k(c, decode_tma_kernel<64>, dim3(grid), dim3(DEC_THREADS), DecSmem<64>::TOTAL, 1, mk, mv, p));
   TB_CUDA(c, cudaGetLastError());
-  decode_combine_kernel<<<d.B * d.H, d.D, 0, c->stream>>>(p, d.D, d.P);
+  TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3(d.B * d.H), dim3(d.D), 0, 1, p, d.D, d.P));
   TB_CUDA(c, cudaGetLastError());
   c->launches += 2;
   return 0;

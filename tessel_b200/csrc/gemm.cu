@@ -39,7 +39,7 @@ namespace {
 enum Epi : int { EPI_F16 = 0, EPI_RESID = 1, EPI_F32 = 2, EPI_GATE_UP = 3 };
 
 constexpr int BM = 128, BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
 constexpr int UNIT_BYTES = 128 * 32 * 4;  // one 128-row x 32-column f32 unit of a partial tile
 
 #ifdef TB200_TRACE
@@ -74,6 +74,7 @@ struct GemmCfg {
   static constexpr int SMEM = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;
   static constexpr int UNITS = MT * (BN / 32);
   static_assert(NB % 16 == 0 && NB <= 256 && COLS <= 512, "UMMA N / TMEM columns");
+  static_assert(BN % 32 == 0 || EPI == EPI_GATE_UP, "only gate_up has a ragged last chunk");
   static_assert(STAGES >= 2, "ring too shallow");
 };
 
@@ -88,11 +89,11 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 #endif
 }
 
-// Writes 32 consecutive columns of one output row (col0 .. col0 + 31, clipped to N).
+// Writes up to 32 consecutive columns of one output row (col0 .. col0 + ncols - 1, clipped to N).
 template <int EPI>
-__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col0, const float* v) {
+__device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int col0, const float* v, int ncols = 32) {
   if (row >= p.M || col0 >= p.N) return;
-  const bool fullw = col0 + 32 <= p.N && (p.N % 8) == 0;
+  const bool fullw = ncols == 32 && col0 + 32 <= p.N && (p.N % 8) == 0;
   if (EPI == EPI_F16 || EPI == EPI_GATE_UP) {
     __half* y = (__half*)p.out + (size_t)row * p.N + col0;
     if (fullw) {
@@ -108,7 +109,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) y[j] = __float2half_rn(v[j]);
+        if (j < ncols && col0 + j < p.N) y[j] = __float2half_rn(v[j]);
     }
   } else {
     float* y = (float*)p.out + (size_t)row * p.N + col0;
@@ -128,7 +129,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N) y[j] = EPI == EPI_RESID ? __fadd_rn(y[j], v[j]) : v[j];
+        if (j < ncols && col0 + j < p.N) y[j] = EPI == EPI_RESID ? __fadd_rn(y[j], v[j]) : v[j];
     }
   }
 }
@@ -156,6 +157,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const int k_begin = (int)((long long)nk * blockIdx.z / S), k_end = (int)((long long)nk * (blockIdx.z + 1) / S);
   const int niter = k_end - k_begin;  // >= 1: the host never asks for more splits than K blocks
 
+  pdl_launch();
   if (threadIdx.x == 0) {
     TB_TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
@@ -180,13 +182,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       prefetch_tmap(&mapB);
       if (EPI == EPI_GATE_UP) prefetch_tmap(&mapB2);
       TB_TRACE(1);
-      for (int i = 0; i < niter; ++i) {
-        const int s = i % STAGES, k = i / STAGES, kc = (k_begin + i) * BK;
-        mbar_wait(&empty[s], (k & 1) ^ 1, p.status, 201);
+      // The weights are not written by any kernel of the stream, so their first tiles are
+      // fetched before waiting for the previous kernel; the activations (A) only after it.
+      const int pre = B_MN ? 0 : (niter < STAGES ? niter : STAGES);
+      auto load_b = [&](int i) {
+        const int s = i % STAGES, kc = (k_begin + i) * BK;
+        unsigned char* b = smem + s * Cfg::STAGE + Cfg::A_BYTES;
         mbar_expect_tx(&full[s], Cfg::STAGE);
-        unsigned char* a = smem + s * Cfg::STAGE;
-        unsigned char* b = a + Cfg::A_BYTES;
-        tma_load_2d(a, &mapA, &full[s], kc, m0);
         if (B_MN) {
           // 64-column blocks of [64 k-rows x 128 bytes] each.
 #pragma unroll
@@ -195,6 +197,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
           tma_load_2d(b, &mapB, &full[s], kc, n0);
           if (EPI == EPI_GATE_UP) tma_load_2d(b + BN * BK * 2, &mapB2, &full[s], kc, n0);
         }
+      };
+      for (int i = 0; i < pre; ++i) load_b(i);
+      pdl_wait();
+      for (int i = 0; i < niter; ++i) {
+        const int s = i % STAGES, k = i / STAGES, kc = (k_begin + i) * BK;
+        if (i >= pre) {
+          mbar_wait(&empty[s], (k & 1) ^ 1, p.status, 201);
+          load_b(i);
+        }
+        tma_load_2d(smem + s * Cfg::STAGE, &mapA, &full[s], kc, m0);
       }
     }
   } else if (warp == 1) {
@@ -224,12 +236,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   }
 
-  // ---- epilogue: warps 2-5, TMEM lane quadrant = warp % 4, one output row per thread ----
+  // ---- epilogue: warps 2-9, TMEM lane quadrant = warp % 4, one output row per thread; the two
+  // warps of a quadrant take alternate column chunks (or exchange units) ----
   const bool epi = warp >= 2;
   const int q = warp & 3;
+  const int eh = (warp - 2) >> 2;
   const uint32_t lane_base = (uint32_t)(q * 32) << 16;
   const bool tracer = warp == 2 && lane == 0;
   if (epi) {
+    pdl_wait();  // the epilogue reads and writes buffers other kernels touch
     mbar_wait(acc_full, 0, p.status, 203);
     tc_fence_after();
     if (tracer) TB_TRACE(4);
@@ -241,6 +256,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const int row = m0 + mt * BM + q * 32 + lane;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (((c0 >> 5) & 1) != eh) continue;
           uint32_t r[32];
           float v[32];
           tmem_ld32(tmem + lane_base + mt * NB + c0, r);
@@ -255,7 +271,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           }
-          store_chunk<EPI>(p, row, n0 + c0, v);
+          store_chunk<EPI>(p, row, n0 + c0, v, BN - c0 < 32 ? BN - c0 : 32);
         }
       }
     }
@@ -272,7 +288,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     if (epi) {
       for (int u = 0; u < Cfg::UNITS; ++u) {
         const uint32_t owner = (uint32_t)(u % S);
-        if (owner == crank) continue;
+        if (owner == crank || ((u / S) & 1) != eh) continue;
         const int mt = u / CH, c0 = (u % CH) * 32;
         uint32_t r[32];
         tmem_ld32(tmem + lane_base + mt * NB + c0, r);
@@ -291,7 +307,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     cluster_sync();  // all partials have landed
     if (tracer) TB_TRACE(7);
     if (epi) {
-      for (int slot = 0; slot < per; ++slot) {
+      for (int slot = eh; slot < per; slot += 2) {
         const int u = slot * S + (int)crank;
         const int mt = u / CH, c0 = (u % CH) * 32;
         uint32_t r[32];
@@ -337,6 +353,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 template <int EPI, bool B_MN>
 __global__ void gemm_plain_kernel(const __half* __restrict__ A, const __half* __restrict__ B,
                                   const __half* __restrict__ B2, void* __restrict__ out, int M, int N, int K) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float sa[32][33], sb[32][33], sb2[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8 threads
   const int m0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
@@ -458,27 +476,16 @@ int run(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, co
   p.K = g.K;
   p.splits = splits;
   p.status = c->status;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((g.M + MT * BM - 1) / (MT * BM), (g.N + BN - 1) / BN, splits);
-  cfg.blockDim = dim3(GEMM_THREADS);
-  cfg.dynamicSmemBytes = Cfg::SMEM;
-  cfg.stream = c->stream;
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeClusterDimension;
-  at[0].val.clusterDim.x = 1;
-  at[0].val.clusterDim.y = 1;
-  at[0].val.clusterDim.z = splits;
-  cfg.attrs = at;
-  cfg.numAttrs = splits > 1 ? 1 : 0;
-  TB_CUDA(c, cudaLaunchKernelEx(&cfg, gemm_kernel<MT, BN, EPI, B_MN>, ma, mb, mb2, p));
+  const dim3 grid((g.M + MT * BM - 1) / (MT * BM), (g.N + BN - 1) / BN, splits);
+  TB_CUDA(c, launch_k(c, gemm_kernel<MT, BN, EPI, B_MN>, grid, dim3(GEMM_THREADS), Cfg::SMEM, splits, ma, mb, mb2, p));
   return 0;
 }
 
 template <int EPI, bool B_MN>
 int run_plain(Ctx* c, const GemmShape& g, const void* A, const void* B, const void* B2, void* out) {
   dim3 grid((g.N + 31) / 32, (g.M + 31) / 32);
-  gemm_plain_kernel<EPI, B_MN><<<grid, 256, 0, c->stream>>>((const __half*)A, (const __half*)B, (const __half*)B2, out,
-                                                            g.M, g.N, g.K);
+  TB_CUDA(c, launch_k(c, gemm_plain_kernel<EPI, B_MN>, dim3(grid), dim3(256), 0, 1, (const __half*)A, (const __half*)B, (const __half*)B2, out,
+                                                            g.M, g.N, g.K));
   TB_CUDA(c, cudaGetLastError());
   return 0;
 }
@@ -488,7 +495,9 @@ template <int MT, int BN>
 int dispatch_epi(Ctx* c, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
                  void* out, bool attr_only) {
   const int epi = epi_of(kind);
-  if (kind == K_MATMUL) {
+  if constexpr (BN == 112) {
+    if (epi == EPI_GATE_UP) return run<MT, BN, EPI_GATE_UP, false>(c, g, splits, A, B, B2, out, attr_only);
+  } else if (kind == K_MATMUL) {
     if constexpr (BN >= 64 && BN != 192) return run<MT, BN, EPI_F16, true>(c, g, splits, A, B, B2, out, attr_only);
   } else if (epi == EPI_GATE_UP) {
     if constexpr (BN <= 128) return run<MT, BN, EPI_GATE_UP, false>(c, g, splits, A, B, B2, out, attr_only);
@@ -507,7 +516,7 @@ int dispatch(Ctx* c, Kind kind, int mt, int bn, const GemmShape& g, int splits, 
 #define TB_CASE(MT_, BN_) \
   if (mt == MT_ && bn == BN_) return dispatch_epi<MT_, BN_>(c, kind, g, splits, A, B, B2, out, attr_only);
   TB_CASE(1, 32) TB_CASE(1, 64) TB_CASE(1, 128) TB_CASE(1, 256)
-  TB_CASE(2, 32) TB_CASE(2, 64) TB_CASE(2, 128) TB_CASE(2, 192) TB_CASE(2, 256)
+  TB_CASE(2, 32) TB_CASE(2, 64) TB_CASE(2, 112) TB_CASE(2, 128) TB_CASE(2, 192) TB_CASE(2, 256)
 #undef TB_CASE
   return fail(c, "gemm: no such tile");
 }
@@ -525,7 +534,7 @@ Plan plan_gemm(Kind kind, const GemmShape& g, int sms) {
   const int epi = epi_of(kind);
   const int out_bytes = epi == EPI_RESID ? 8 : (epi == EPI_F32 ? 4 : 2);
   const int nbf = epi == EPI_GATE_UP ? 2 : 1;
-  const int bns[] = {256, 192, 128, 64, 32};
+  const int bns[] = {256, 192, 128, 112, 64, 32};
   Plan best = {1, 64, 1, 1e30};
   for (int mt = 1; mt <= 2; ++mt) {
     if (mt == 2 && g.M <= BM) continue;
@@ -533,6 +542,7 @@ Plan plan_gemm(Kind kind, const GemmShape& g, int sms) {
       if (kind == K_MATMUL && (bn < 64 || bn == 192)) continue;
       if (epi == EPI_GATE_UP && bn > 128) continue;
       if (bn == 192 && mt == 1) continue;
+      if (bn == 112 && (mt == 1 || epi != EPI_GATE_UP)) continue;
       const int nb = bn * nbf;
       if (mt * nb > 512) continue;
       const int stage = mt * BM * BK * 2 + nb * BK * 2;

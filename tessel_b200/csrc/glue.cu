@@ -34,6 +34,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // kernels/llm.tl:10-16. One block per token; a token outside [0, V) reads zeros.
 __global__ void embed_kernel(const int* __restrict__ tok, const __half* __restrict__ E, float* __restrict__ X, int V,
                              int Dm) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int row = tok[t];
   const bool in = row >= 0 && row < V;
@@ -59,6 +61,8 @@ __global__ void embed_kernel(const int* __restrict__ tok, const __half* __restri
 template <int PER>  // float4 chunks per thread
 __global__ void rmsnorm_kernel(const float* __restrict__ X, const int* __restrict__ idx, const __half* __restrict__ W,
                                __half* __restrict__ Y, float eps, int T, int Dm) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[32];
   const int b = blockIdx.x;
   int r = idx ? idx[b] : b;
@@ -99,6 +103,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ X, const int* __restric
 // Any Dm (two passes over the row).
 __global__ void rmsnorm_generic_kernel(const float* __restrict__ X, const int* __restrict__ idx,
                                        const __half* __restrict__ W, __half* __restrict__ Y, float eps, int T, int Dm) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float red[32];
   const int b = blockIdx.x;
   int r = idx ? idx[b] : b;
@@ -150,6 +156,8 @@ __device__ __forceinline__ void rotate8(const H8& x1, const H8& x2, const float*
 __global__ void rope_q_kernel(const __half* __restrict__ QKV, const int* __restrict__ pos, const float* __restrict__ Ct,
                               const float* __restrict__ St, __half* __restrict__ Q, int T, int W, int NPOS, int H,
                               int D) {
+  pdl_launch();
+  pdl_wait();
   const int d2 = D >> 1, per = d2 >> 3;  // 8-pair chunks per head
   const long long n = (long long)T * H * per;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -178,6 +186,8 @@ __global__ void kv_write_kernel(const __half* __restrict__ QKV, const int* __res
                                 const float* __restrict__ St, __half* __restrict__ Kc, __half* __restrict__ Vc,
                                 __half* __restrict__ Kd, __half* __restrict__ Vd, int T, int W, int NPOS, int NS, int G,
                                 int D) {
+  pdl_launch();
+  pdl_wait();
   const int d2 = D >> 1, per = d2 >> 3;
   const long long n = (long long)T * G * per;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -212,6 +222,8 @@ __global__ void kv_write_kernel(const __half* __restrict__ QKV, const int* __res
 
 // R += P, f32, n % 4 == 0.
 __global__ void residual_add_kernel(float* __restrict__ R, const float* __restrict__ P, long long n4) {
+  pdl_launch();
+  pdl_wait();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float4 r = reinterpret_cast<float4*>(R)[i];
     const float4 p = reinterpret_cast<const float4*>(P)[i];
@@ -223,6 +235,8 @@ __global__ void residual_add_kernel(float* __restrict__ R, const float* __restri
 // First index of each row's maximum (src/llm/mod.rs:132-140: a later equal
 // value does not replace an earlier one; NaN never wins). One block per row.
 __global__ void argmax_rows_kernel(const float* __restrict__ X, int* __restrict__ out, int N) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float bv[32];
   __shared__ int bi[32];
   const float* x = X + (size_t)blockIdx.x * N;
@@ -275,6 +289,8 @@ __global__ void argmax_rows_kernel(const float* __restrict__ X, int* __restrict_
 __global__ void decode_advance_kernel(const int* __restrict__ picked, int* __restrict__ tok, int* __restrict__ pos,
                                       int* __restrict__ slot, int* __restrict__ lens, const int* __restrict__ table,
                                       int* __restrict__ hist, int MP, int n, int P) {
+  pdl_launch();
+  pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= n) return;
   const int p = pos[b] + 1;
@@ -351,7 +367,7 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
     case K_EMBED: {
       const int T = (int)s[0][0], V = (int)s[1][0], Dm = (int)s[1][1];
       if (T == 0) return 0;
-      embed_kernel<<<T, 128, 0, st>>>((const int*)a[0], (const __half*)a[1], (float*)a[2], V, Dm);
+      TB_CUDA(c, launch_k(c, embed_kernel, dim3(T), dim3(128), 0, 1, (const int*)a[0], (const __half*)a[1], (float*)a[2], V, Dm));
       break;
     }
     case K_RMSNORM:
@@ -367,24 +383,24 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
       const float eps = bits_f32(a[rows ? 4 : 3]);
       const int chunks = Dm / 4;
       if (chunks <= 256)
-        rmsnorm_kernel<1><<<B, 256, 0, st>>>(X, idx, W, Y, eps, T, Dm);
+        TB_CUDA(c, launch_k(c, rmsnorm_kernel<1>, dim3(B), dim3(256), 0, 1, X, idx, W, Y, eps, T, Dm));
       else if (chunks <= 512)
-        rmsnorm_kernel<2><<<B, 256, 0, st>>>(X, idx, W, Y, eps, T, Dm);
+        TB_CUDA(c, launch_k(c, rmsnorm_kernel<2>, dim3(B), dim3(256), 0, 1, X, idx, W, Y, eps, T, Dm));
       else if (chunks <= 1024)
-        rmsnorm_kernel<4><<<B, 256, 0, st>>>(X, idx, W, Y, eps, T, Dm);
+        TB_CUDA(c, launch_k(c, rmsnorm_kernel<4>, dim3(B), dim3(256), 0, 1, X, idx, W, Y, eps, T, Dm));
       else if (chunks <= 2048)
-        rmsnorm_kernel<8><<<B, 256, 0, st>>>(X, idx, W, Y, eps, T, Dm);
+        TB_CUDA(c, launch_k(c, rmsnorm_kernel<8>, dim3(B), dim3(256), 0, 1, X, idx, W, Y, eps, T, Dm));
       else
-        rmsnorm_generic_kernel<<<B, 256, 0, st>>>(X, idx, W, Y, eps, T, Dm);
+        TB_CUDA(c, launch_k(c, rmsnorm_generic_kernel, dim3(B), dim3(256), 0, 1, X, idx, W, Y, eps, T, Dm));
       break;
     }
     case K_ROPE_Q: {
       const int T = (int)s[0][0], W = (int)s[0][1], NPOS = (int)s[2][0], H = (int)s[4][1], D = (int)s[4][2];
       const long long n = (long long)T * H * (D / 16);
       if (n == 0) return 0;
-      rope_q_kernel<<<grid_for(n, 256, c->sm_count), 256, 0, st>>>((const __half*)a[0], (const int*)a[1],
+      TB_CUDA(c, launch_k(c, rope_q_kernel, dim3(grid_for(n, 256, c->sm_count)), dim3(256), 0, 1, (const __half*)a[0], (const int*)a[1],
                                                                    (const float*)a[2], (const float*)a[3],
-                                                                   (__half*)a[4], T, W, NPOS, H, D);
+                                                                   (__half*)a[4], T, W, NPOS, H, D));
       break;
     }
     case K_KV_WRITE: {
@@ -392,9 +408,9 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
                 D = (int)s[5][2];
       const long long n = (long long)T * G * (D / 16);
       if (n == 0) return 0;
-      kv_write_kernel<<<grid_for(n, 128, c->sm_count), 128, 0, st>>>(
+      TB_CUDA(c, launch_k(c, kv_write_kernel, dim3(grid_for(n, 128, c->sm_count)), dim3(128), 0, 1, 
           (const __half*)a[0], (const int*)a[1], (const int*)a[2], (const float*)a[3], (const float*)a[4],
-          (__half*)a[5], (__half*)a[6], (__half*)a[7], (__half*)a[8], T, W, NPOS, NS, G, D);
+          (__half*)a[5], (__half*)a[6], (__half*)a[7], (__half*)a[8], T, W, NPOS, NS, G, D));
       break;
     }
     case K_RESIDUAL_ADD: {
@@ -402,13 +418,13 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
       for (int64_t d : s[0]) n *= d;
       if (n % 4) return fail(c, "residual_add: element count must be a multiple of 4");
       if (n == 0) return 0;
-      residual_add_kernel<<<grid_for(n / 4, 256, c->sm_count), 256, 0, st>>>((float*)a[0], (const float*)a[1], n / 4);
+      TB_CUDA(c, launch_k(c, residual_add_kernel, dim3(grid_for(n / 4, 256, c->sm_count)), dim3(256), 0, 1, (float*)a[0], (const float*)a[1], n / 4));
       break;
     }
     case K_ARGMAX_ROWS: {
       const int M = (int)s[0][0], N = (int)s[0][1];
       if (M == 0) return 0;
-      argmax_rows_kernel<<<M, 1024, 0, st>>>((const float*)a[0], (int*)a[1], N);
+      TB_CUDA(c, launch_k(c, argmax_rows_kernel, dim3(M), dim3(1024), 0, 1, (const float*)a[0], (int*)a[1], N));
       break;
     }
     case K_DECODE_ADVANCE: {
@@ -417,9 +433,9 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
       if (n < 0 || n > T || P < 1) return fail(c, "decode_advance: 0 <= n <= T and P >= 1");
       if (step < 0 || step >= (int)s[6][0]) return fail(c, "decode_advance: step outside the history");
       if (n == 0) return 0;
-      decode_advance_kernel<<<(n + 127) / 128, 128, 0, st>>>((const int*)a[0], (int*)a[1], (int*)a[2], (int*)a[3],
+      TB_CUDA(c, launch_k(c, decode_advance_kernel, dim3((n + 127) / 128), dim3(128), 0, 1, (const int*)a[0], (int*)a[1], (int*)a[2], (int*)a[3],
                                                              (int*)a[4], (const int*)a[5], (int*)a[6] + (size_t)step * T,
-                                                             MP, n, P);
+                                                             MP, n, P));
       break;
     }
     default:

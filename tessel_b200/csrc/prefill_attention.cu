@@ -59,6 +59,8 @@ template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
     fa_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
               const __grid_constant__ CUtensorMap mapV, const FaParams p) {
+  pdl_launch();
+  pdl_wait();
   using SM = FaSmem<D>;
   constexpr int SUB = SM::SUB;
   extern __shared__ unsigned char smem_raw[];
@@ -312,6 +314,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
 __global__ void fa_generic_kernel(const __half* __restrict__ Q, const __half* __restrict__ K,
                                   const __half* __restrict__ V, const int* __restrict__ starts, __half* __restrict__ O,
                                   float scale, int S, int H, int G, int D, int plain) {
+  pdl_launch();
+  pdl_wait();
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (w >= (long long)S * H) return;
@@ -406,7 +410,7 @@ int run_fa(Ctx* c, const FaShape& f, const void* Q, const void* K, const void* V
   p.plain = f.plain;
   p.status = c->status;
   dim3 grid((f.S + FA_TILES * FA_BM - 1) / (FA_TILES * FA_BM), f.H);
-  fa_kernel<D><<<grid, FA_THREADS, FaSmem<D>::TOTAL, c->stream>>>(mq, mk, mv, p);
+  TB_CUDA(c, launch_k(c, fa_kernel<D>, dim3(grid), dim3(FA_THREADS), FaSmem<D>::TOTAL, 1, mq, mk, mv, p));
   TB_CUDA(c, cudaGetLastError());
   return 0;
 }
@@ -448,9 +452,9 @@ int launch_prefill(Ctx* c, Op& op, const uint64_t* a) {
     r = f.D == 128 ? run_fa<128>(c, f, Q, K, V, starts, O, scale) : run_fa<64>(c, f, Q, K, V, starts, O, scale);
   } else {
     const long long warps = (long long)f.S * f.H;
-    fa_generic_kernel<<<(unsigned)((warps + 3) / 4), 128, 0, c->stream>>>((const __half*)Q, (const __half*)K,
+    TB_CUDA(c, launch_k(c, fa_generic_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, 1, (const __half*)Q, (const __half*)K,
                                                                           (const __half*)V, starts, (__half*)O, scale,
-                                                                          f.S, f.H, f.G, f.D, f.plain);
+                                                                          f.S, f.H, f.G, f.D, f.plain));
     cudaError_t e = cudaGetLastError();
     r = e == cudaSuccess ? 0 : cuda_fail(c, e, "fa_generic_kernel");
   }

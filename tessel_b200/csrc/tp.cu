@@ -74,6 +74,8 @@ template <int PER>  // float4 chunks per thread: dim <= PER * 4096
 __global__ void __launch_bounds__(TP_THREADS, 1)
     tp_reduce_norm_kernel(const TpTable* __restrict__ table, const __half* __restrict__ W, float eps, int T, int dim,
                           int which, int do_norm, unsigned int* status) {
+  pdl_launch();
+  pdl_wait();
   __shared__ TpTable tb_;
   __shared__ float red[32];
   __shared__ unsigned int s_epoch;
@@ -191,11 +193,11 @@ int launch_tp(Ctx* c, Op& op, const uint64_t* a) {
   if (grid > c->sm_count) grid = c->sm_count;
   if (grid > TP_SLOTS) grid = TP_SLOTS;
   if (dim <= 4 * TP_THREADS)
-    tp_reduce_norm_kernel<1><<<grid, TP_THREADS, 0, c->stream>>>((const TpTable*)a[0], (const __half*)a[1], eps, T,
-                                                                 dim, which, do_norm, c->status);
+    TB_CUDA(c, launch_k(c, tp_reduce_norm_kernel<1>, dim3(grid), dim3(TP_THREADS), 0, 1, (const TpTable*)a[0], (const __half*)a[1], eps, T,
+                                                                 dim, which, do_norm, c->status));
   else
-    tp_reduce_norm_kernel<2><<<grid, TP_THREADS, 0, c->stream>>>((const TpTable*)a[0], (const __half*)a[1], eps, T,
-                                                                 dim, which, do_norm, c->status);
+    TB_CUDA(c, launch_k(c, tp_reduce_norm_kernel<2>, dim3(grid), dim3(TP_THREADS), 0, 1, (const TpTable*)a[0], (const __half*)a[1], eps, T,
+                                                                 dim, which, do_norm, c->status));
   TB_CUDA(c, cudaGetLastError());
   c->launches += 1;
   return 0;

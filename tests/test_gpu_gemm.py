@@ -123,6 +123,17 @@ def test_forced_tiles_and_cluster_split_k(gpu, plan, M, N, K, monkeypatch):
         assert rel_err(y[rows], oracle.gate_up(x[rows], w, wu)) <= TOL
 
 
+def test_gate_up_ragged_tile(gpu, monkeypatch):
+    """The 112-column gate_up tile (224-wide MMA, last epilogue chunk 16 columns wide), which lets
+    14336 MLP columns fill 128 SMs in one wave; columns beyond a tile must not be written."""
+    monkeypatch.setenv("TB200_GEMM_PLAN", "2,112,1")
+    r = oracle.Rng(34)
+    M, F, K = 256, 1000, 512  # 9 tiles of 112, the last one partial
+    x, wg, wu = r.tensor(h, (M, K)), r.tensor(h, (F, K), 0.1), r.tensor(h, (F, K), 0.1)
+    y = launch(gpu, "gate_up", [x, wg, wu, np.zeros((M, F), h)], 3)
+    assert rel_err(y, oracle.gate_up(x, wg, wu)) <= TOL
+
+
 def test_empty_shapes(gpu):
     x = np.zeros((0, 64), h)
     w = np.ones((32, 64), h)
