@@ -74,7 +74,8 @@ int tb200_host_free(tb200_ctx* ctx, void* ptr);
  * matmul (kernels/matmul.tl:3-17), flash_attention, paged_attention
  * (kernels/attention.tl:4-51); and, with no counterpart in the reference,
  * linear_f32 (X[M,K], W[N,K], Y f32[M,N]), residual_add (R f32[M,N], P
- * f32[M,N]), argmax_rows (X f32[M,N], out i32[M]) and decode_advance
+ * f32[M,N]), argmax_rows (X f32[M,N], out i32[M]), rope_kv (rope_q and kv_write
+ * in one launch: QKV, pos, slot, C, S, Q, Kc, Vc, K, V) and decode_advance
  * (picked[T], tok[T], pos[T], slot[T], lens[T], table[T,MP], hist[S,T], then
  * the i32 scalars n, P and step: the next decode step's inputs for rows < n,
  * computed on the device as src/llm/sched.rs:139-144 computes them on the

@@ -38,6 +38,7 @@ enum Kind : int {
   K_LINEAR_F32,     // Y f32 = X W^T (a tensor-parallel rank's partial product)
   K_RESIDUAL_ADD,   // R f32 += P f32
   K_ARGMAX_ROWS,    // first index of each row's maximum
+  K_ROPE_KV,        // rope_q and kv_write in one launch
   K_TP_REDUCE_NORM, // cross-rank sum of partial products + residual add + RMSNorm over peer memory
   K_DECODE_ADVANCE, // next decode step's tok/pos/slot/lens from this step's picks, on the device
   K_COUNT

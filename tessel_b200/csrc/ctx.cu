@@ -82,6 +82,7 @@ static const KindInfo KINDS[] = {
     {"argmax_rows", K_ARGMAX_ROWS, 2, 2},
     {"decode_advance", K_DECODE_ADVANCE, 7, 10},
     {"tp_reduce_norm", K_TP_REDUCE_NORM, 3, 7},
+    {"rope_kv", K_ROPE_KV, 10, 10},
 };
 
 static bool is_gemm(Kind k) {

@@ -276,25 +276,44 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
 // Merges the split partials of one (sequence, head): O = f16(sum_s acc_s w_s / sum_s l_s w_s).
 // A sequence with lens == 0 has no partial and gives 0/0 = NaN, as the
 // reference does (kernels/llm.tl:172 with l == 0).
+// One warp per (sequence, head), eight per block; a lane owns D/32 consecutive columns.
 __global__ void decode_combine_kernel(const DecodeParams p, int D, int P) {
   pdl_launch();
   pdl_wait();
-  const int bh = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int bh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (bh >= p.B * p.H) return;
   const int b = bh / p.H;
   const int n = p.lens[b];
   const int npages = n > 0 ? (n + P - 1) / P : 0;
   const int ns = (npages + p.chunk - 1) / p.chunk;
+  const float* ml = p.part_ml + (size_t)bh * p.nsplit * 2;
   float mt = -INFINITY;
-  for (int s = 0; s < ns; ++s) mt = fmaxf(mt, p.part_ml[((size_t)bh * p.nsplit + s) * 2]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float lt = 0.f, at = 0.f;
-    for (int s = 0; s < ns; ++s) {
-      const size_t o = (size_t)bh * p.nsplit + s;
-      const float w = exp2f(p.part_ml[o * 2] - mt);
-      lt += p.part_ml[o * 2 + 1] * w;
-      at += p.part_acc[o * D + d] * w;
+  for (int s = lane; s < ns; s += 32) mt = fmaxf(mt, ml[s * 2]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+  const int V = D >> 5;  // 2 or 4 on the paths that use this kernel
+  const float* acc = p.part_acc + (size_t)bh * p.nsplit * D + lane * V;
+  float lt = 0.f, at[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < ns; ++s) {
+    const float w = exp2f(ml[s * 2] - mt);
+    lt += ml[s * 2 + 1] * w;
+    if (V == 4) {
+      const float4 a = *reinterpret_cast<const float4*>(acc + (size_t)s * D);
+      at[0] += a.x * w, at[1] += a.y * w, at[2] += a.z * w, at[3] += a.w * w;
+    } else {
+      const float2 a = *reinterpret_cast<const float2*>(acc + (size_t)s * D);
+      at[0] += a.x * w, at[1] += a.y * w;
     }
-    p.O[(size_t)bh * D + d] = __float2half_rn(at / lt);
+  }
+  __half* o = p.O + (size_t)bh * D + lane * V;
+  if (V == 4) {
+    uint2 y;
+    y.x = pack_h2(at[0] / lt, at[1] / lt);
+    y.y = pack_h2(at[2] / lt, at[3] / lt);
+    *reinterpret_cast<uint2*>(o) = y;
+  } else {
+    *reinterpret_cast<uint32_t*>(o) = pack_h2(at[0] / lt, at[1] / lt);
   }
 }
 
@@ -448,7 +467,7 @@ int launch_decode(Ctx* c, Op& op, const uint64_t* a) {
   else
     TB_CUDA(c, launch_k(c, decode_tma_kernel<64>, dim3(grid), dim3(DEC_THREADS), DecSmem<64>::TOTAL, 1, mk, mv, p));
   TB_CUDA(c, cudaGetLastError());
-  TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3(d.B * d.H), dim3(d.D), 0, 1, p, d.D, d.P));
+  TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3((d.B * d.H + 7) / 8), dim3(256), 0, 1, p, d.D, d.P));
   TB_CUDA(c, cudaGetLastError());
   c->launches += 2;
   return 0;
@@ -571,7 +590,7 @@ extern "C" int tb200_decode_attention_static(tb200_ctx* h, const int32_t* dims, 
   else
     TB_CUDA(c, launch_k(c, decode_tma_kernel<64>, dim3(grid), dim3(DEC_THREADS), DecSmem<64>::TOTAL, 1, mk, mv, p));
   TB_CUDA(c, cudaGetLastError());
-  TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3(d.B * d.H), dim3(d.D), 0, 1, p, d.D, d.P));
+  TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3((d.B * d.H + 7) / 8), dim3(256), 0, 1, p, d.D, d.P));
   TB_CUDA(c, cudaGetLastError());
   c->launches += 2;
   return 0;

@@ -220,6 +220,58 @@ __global__ void kv_write_kernel(const __half* __restrict__ QKV, const int* __res
   }
 }
 
+// rope_q and kv_write in one launch (kernels/llm.tl:78-112): unit = 8 pairs of one (token, head),
+// query heads first, then KV heads.
+__global__ void rope_kv_kernel(const __half* __restrict__ QKV, const int* __restrict__ pos,
+                               const int* __restrict__ slot, const float* __restrict__ Ct,
+                               const float* __restrict__ St, __half* __restrict__ Q, __half* __restrict__ Kc,
+                               __half* __restrict__ Vc, __half* __restrict__ Kd, __half* __restrict__ Vd, int T, int W,
+                               int NPOS, int NS, int H, int G, int D) {
+  pdl_launch();
+  pdl_wait();
+  const int d2 = D >> 1, per = d2 >> 3, HG = H + G;
+  const long long n = (long long)T * HG * per;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int ch = (int)(i % per);
+    const int hh = (int)((i / per) % HG);
+    const int t = (int)(i / ((long long)per * HG));
+    const int p = pos[t];
+    const bool in = p >= 0 && p < NPOS;
+    const size_t to = (size_t)(in ? p : 0) * d2 + ch * 8;
+    H8 x1, x2, y1, y2;
+    if (hh < H) {
+      const __half* src = QKV + (size_t)t * W + hh * D + ch * 8;
+      x1.u = *reinterpret_cast<const uint4*>(src);
+      x2.u = *reinterpret_cast<const uint4*>(src + d2);
+      rotate8(x1, x2, Ct + to, St + to, in, y1, y2);
+      __half* dst = Q + ((size_t)t * H + hh) * D + ch * 8;
+      *reinterpret_cast<uint4*>(dst) = y1.u;
+      *reinterpret_cast<uint4*>(dst + d2) = y2.u;
+    } else {
+      const int g = hh - H, at = slot[t];
+      const bool keep = at >= 0 && at < NS;
+      const __half* src = QKV + (size_t)t * W + (W - 2 * G * D + g * D) + ch * 8;
+      x1.u = *reinterpret_cast<const uint4*>(src);
+      x2.u = *reinterpret_cast<const uint4*>(src + d2);
+      const uint4 v1 = *reinterpret_cast<const uint4*>(src + G * D);
+      const uint4 v2 = *reinterpret_cast<const uint4*>(src + G * D + d2);
+      rotate8(x1, x2, Ct + to, St + to, in, y1, y2);
+      const size_t dd = ((size_t)t * G + g) * D + ch * 8;
+      *reinterpret_cast<uint4*>(Kd + dd) = y1.u;
+      *reinterpret_cast<uint4*>(Kd + dd + d2) = y2.u;
+      *reinterpret_cast<uint4*>(Vd + dd) = v1;
+      *reinterpret_cast<uint4*>(Vd + dd + d2) = v2;
+      if (keep) {
+        const size_t cd = ((size_t)at * G + g) * D + ch * 8;
+        *reinterpret_cast<uint4*>(Kc + cd) = y1.u;
+        *reinterpret_cast<uint4*>(Kc + cd + d2) = y2.u;
+        *reinterpret_cast<uint4*>(Vc + cd) = v1;
+        *reinterpret_cast<uint4*>(Vc + cd + d2) = v2;
+      }
+    }
+  }
+}
+
 // R += P, f32, n % 4 == 0.
 __global__ void residual_add_kernel(float* __restrict__ R, const float* __restrict__ P, long long n4) {
   pdl_launch();
@@ -344,6 +396,16 @@ int make_glue(Ctx* c, Op& op) {
       if (s[6] != s[5] || s[8] != s[7] || s[7][1] != G || s[7][2] != D) return bad("K/V shapes disagree");
       break;
     }
+    case K_ROPE_KV: {
+      // QKV[T,W], pos[T], slot[T], C, S [NPOS,D/2], Q[T,H,D], Kc, Vc [NS,G,D], K, V [T,G,D]
+      if (s[0].size() != 2 || s[5].size() != 3 || s[6].size() != 3 || s[8].size() != 3 || s[3].size() != 2)
+        return bad("shapes are QKV[T,W], pos[T], slot[T], C, S, Q[T,H,D], Kc, Vc[NS,G,D], K, V[T,G,D]");
+      const int64_t H = s[5][1], D = s[5][2], G = s[6][1];
+      if (D % 16 || s[3][1] != D / 2 || s[4] != s[3]) return bad("head_dim must be a multiple of 16, tables [NPOS, D/2]");
+      if (s[0][1] % 8 || s[0][1] != (H + 2 * G) * D) return bad("W must be (H + 2G) * D");
+      if (s[7] != s[6] || s[9] != s[8] || s[6][2] != D || s[8][1] != G || s[8][2] != D) return bad("K/V shapes disagree");
+      break;
+    }
     case K_RESIDUAL_ADD:
       if (s[0] != s[1]) return bad("R and P must have one shape");
       break;
@@ -411,6 +473,16 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
       TB_CUDA(c, launch_k(c, kv_write_kernel, dim3(grid_for(n, 128, c->sm_count)), dim3(128), 0, 1, 
           (const __half*)a[0], (const int*)a[1], (const int*)a[2], (const float*)a[3], (const float*)a[4],
           (__half*)a[5], (__half*)a[6], (__half*)a[7], (__half*)a[8], T, W, NPOS, NS, G, D));
+      break;
+    }
+    case K_ROPE_KV: {
+      const int T = (int)s[0][0], W = (int)s[0][1], NPOS = (int)s[3][0], H = (int)s[5][1], D = (int)s[5][2],
+                NS = (int)s[6][0], G = (int)s[6][1];
+      const long long n = (long long)T * (H + G) * (D / 16);
+      if (n == 0) return 0;
+      TB_CUDA(c, launch_k(c, rope_kv_kernel, dim3(grid_for(n, 128, c->sm_count)), dim3(128), 0, 1, (const __half*)a[0],
+                          (const int*)a[1], (const int*)a[2], (const float*)a[3], (const float*)a[4], (__half*)a[5],
+                          (__half*)a[6], (__half*)a[7], (__half*)a[8], (__half*)a[9], T, W, NPOS, NS, H, G, D));
       break;
     }
     case K_RESIDUAL_ADD: {

@@ -325,9 +325,9 @@ class Engine:
         embed = k("embed", [[t], [v, dm], [t, dm]])
         norm = k("rmsnorm", [[t, dm], [dm], [t, dm]])
         qkv = k("linear", [[t, dm], [w, dm], [t, w]])
-        rope = k("rope_q", [[t, w], [t], [npos, hd // 2], [npos, hd // 2], [t, nh, hd]])
-        kvw = k("kv_write", [[t, w], [t], [t], [npos, hd // 2], [npos, hd // 2], [ns, ng, hd], [ns, ng, hd],
-                             [t, ng, hd], [t, ng, hd]])
+        # rope_q and kv_write of the reference (src/llm/engine.rs:391-418) run as one launch.
+        ropekv = k("rope_kv", [[t, w], [t], [t], [npos, hd // 2], [npos, hd // 2], [t, nh, hd], [ns, ng, hd],
+                               [ns, ng, hd], [t, ng, hd], [t, ng, hd]])
         if prefill:
             att = k("prefill_attention", [[t, nh, hd], [t, ng, hd], [t, ng, hd], [t], [t, nh, hd]])
         else:
@@ -349,14 +349,13 @@ class Engine:
 
         g.launch(embed, [self.tok, self.embed, self.x])
         if self.tp_table is not None:
-            self._launch_layers_fused(t, prefill, norm, qkv, rope, kvw, att, oproj, gu, down, eps, scale)
+            self._launch_layers_fused(t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale)
             self._launch_head(t, bw, greedy, eps)
             return
         for l in self.layers:
             g.launch(norm, [self.x, l.n1, self.h, eps])
             g.launch(qkv, [self.h, l.wqkv, self.qkv])
-            g.launch(rope, [self.qkv, self.pos, self.cos, self.sin, self.q])
-            g.launch(kvw, [self.qkv, self.pos, self.slot, self.cos, self.sin, l.kc, l.vc, self.k, self.v])
+            g.launch(ropekv, [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l.kc, l.vc, self.k, self.v])
             if prefill:
                 g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
             else:
@@ -367,7 +366,7 @@ class Engine:
             project(down, self.mlp, l.wd)
         self._launch_head(t, bw, greedy, eps)
 
-    def _launch_layers_fused(self, t, prefill, norm, qkv, rope, kvw, att, oproj, gu, down, eps, scale) -> None:
+    def _launch_layers_fused(self, t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale) -> None:
         """The decoder layers under tensor parallelism with the fused cross-rank reduction: each
         projection pair ends in one ``tp_reduce_norm`` that sums the ranks' partials into the
         residual stream and writes the next layer input h on every rank."""
@@ -377,8 +376,7 @@ class Engine:
         g.launch(norm, [self.x, self.layers[0].n1, self.h, eps])
         for i, l in enumerate(self.layers):
             g.launch(qkv, [self.h, l.wqkv, self.qkv])
-            g.launch(rope, [self.qkv, self.pos, self.cos, self.sin, self.q])
-            g.launch(kvw, [self.qkv, self.pos, self.slot, self.cos, self.sin, l.kc, l.vc, self.k, self.v])
+            g.launch(ropekv, [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l.kc, l.vc, self.k, self.v])
             if prefill:
                 g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
             else:

@@ -124,6 +124,11 @@ class EmuGpu:
             kc, vc, kd, vd = oracle.kv_write(A(0, h), A(1, i), A(2, i), A(3, f), A(4, f), A(5, h), A(6, h), sh[5][1],
                                              sh[5][2])
             A(5, h)[:], A(6, h)[:], A(7, h)[:], A(8, h)[:] = kc, vc, kd, vd
+        elif name == "rope_kv":
+            A(5, h)[:] = oracle.rope_q(A(0, h), A(1, i), A(3, f), A(4, f), sh[5][1], sh[5][2])
+            kc, vc, kd, vd = oracle.kv_write(A(0, h), A(1, i), A(2, i), A(3, f), A(4, f), A(6, h), A(7, h), sh[6][1],
+                                             sh[6][2])
+            A(6, h)[:], A(7, h)[:], A(8, h)[:], A(9, h)[:] = kc, vc, kd, vd
         elif name == "prefill_attention":
             A(4, h)[:] = oracle.prefill_attention(A(0, h), A(1, h), A(2, h), A(3, i), sc(5))
         elif name == "flash_attention":

@@ -82,6 +82,11 @@ def test_rope_q_and_kv_write_bit_exact(gpu, T, H, G, D, NPOS):
     wkc, wvc, wkd, wvd = oracle.kv_write(qkv, pos, slot, Ct, St, kc0, vc0, G, D)
     for got, want in ((kc, wkc), (vc, wvc), (kd, wkd), (vd, wvd)):
         assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    # The engine's one-launch form of the two kernels gives the same bits.
+    q2, kc2, vc2, kd2, vd2 = run(gpu, "rope_kv", [qkv, pos, slot, Ct, St, np.zeros((T, H, D), h), kc0, vc0,
+                                                  np.zeros((T, G, D), h), np.zeros((T, G, D), h)], [5, 6, 7, 8, 9])
+    for got, want in ((q2, q), (kc2, wkc), (vc2, wvc), (kd2, wkd), (vd2, wvd)):
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
 
 
 def test_residual_add_and_argmax(gpu):
