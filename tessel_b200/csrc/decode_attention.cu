@@ -402,6 +402,7 @@ int make_decode(Ctx* c, Op& op) {
   const int hgroups = (d.H / d.G + 7) / 8;
   const long long units = (long long)d.B * d.G * hgroups;
   long long want = (4LL * c->sm_count + units - 1) / units;
+  if (const char* e = getenv("TB200_DECODE_SPLITS")) want = atoi(e);  // tuning and tests
   const int max_split = (d.MP + 3) / 4;
   int nsplit = (int)(want < 1 ? 1 : (want > max_split ? max_split : want));
   int chunk = (d.MP + nsplit - 1) / nsplit;

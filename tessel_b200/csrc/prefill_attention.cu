@@ -7,9 +7,10 @@
 // A producer warp brings both Q tiles once and then 128-key K and V tiles through a two-stage
 // TMA ring. One thread issues the MMAs: S_t = Q_t K^T (M 128, N 128) into tensor memory, and
 // O_t += P_t V (M 128, N D) with P read straight from tensor memory and O accumulated there.
-// Each tile has a softmax warpgroup, one query row per thread: it reads S out of tensor memory,
-// applies scale and the causal / sequence-start mask, rounds P to f16 (as kernels/llm.tl:143
-// does) and stores it over S's first columns. The MMA order S0 S1 | PV0 S0' | PV1 S1' | ... lets
+// Each tile has eight softmax warps: a thread owns one query row and half of the block's keys
+// (the two warps of a row exchange their row maxima through shared memory); it reads S out of
+// tensor memory, applies scale and the causal / sequence-start mask, rounds P to f16 (as
+// kernels/llm.tl:143 does) and stores it over S's first columns. The MMA order S0 S1 | PV0 S0' | PV1 S1' | ... lets
 // one tile's softmax run while the tensor pipe works on the other tile. The running maximum is
 // lazy: O (in tensor memory) is rescaled only when a row's maximum grew by more than 2^8, which
 // leaves P <= 256 and changes no result beyond rounding; the final division by the row sum is
@@ -28,9 +29,27 @@ namespace {
 constexpr int FA_BM = 128;        // query rows per tile (one MMA's M)
 constexpr int FA_TILES = 2;       // query tiles per CTA: two softmax warpgroups take turns on the tensor pipe
 constexpr int FA_BN = 128;        // keys per block
-constexpr int FA_THREADS = 320;   // warp 0 TMA, warp 1 MMA, warps 2-5 and 6-9 softmax
+constexpr int FA_THREADS = 576;   // warp 0 TMA, warp 1 MMA, warps 2-9 and 10-17 softmax of tile 0 and 1
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;  // O is rescaled only when a row's maximum grew by more than 2^8
+
+// 2^x on the special-function unit.
+__device__ __forceinline__ float exp2_sfu(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+#ifdef TB200_TRACE
+__device__ unsigned long long* g_fa_trace = nullptr;  // [kind][block] timestamps (ns) of CTA (0, 0); development builds only
+#define FA_TRACE(kind, jb)                                                                \
+  do {                                                                                    \
+    if (g_fa_trace && blockIdx.x == 0 && blockIdx.y == 0 && (jb) < 64) g_fa_trace[(kind) * 64 + (jb)] = globaltimer(); \
+  } while (0)
+#else
+#define FA_TRACE(kind, jb) \
+  do {                     \
+  } while (0)
+#endif
 
 struct FaParams {
   const int* starts;  // null for the plain layout
@@ -49,7 +68,8 @@ struct FaSmem {
   static constexpr int STAGE = 2 * KV_BYTES;
   static constexpr int OFF_KV = Q_BYTES;
   static constexpr int OFF_BAR = OFF_KV + 2 * STAGE;
-  static constexpr int TOTAL = OFF_BAR + 16 * 8 + 1024;
+  static constexpr int OFF_XCH = OFF_BAR + 16 * 8;  // row maxima / sums exchanged between half-row warps
+  static constexpr int TOTAL = OFF_XCH + FA_TILES * 2 * FA_BM * 4 + 1024;
   // Tensor memory: S of tile t at columns [128 t, 128 t + 128) (its first 64 columns are
   // reused for P as packed f16 pairs), O of tile t at [256 + D t, 256 + D t + D).
   static constexpr int TMEM_COLS = 512;
@@ -94,7 +114,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 128);
+      mbar_init(&p_ready[i], 256);
       mbar_init(&o_done[i], 1);
     }
     fence_barrier_init();
@@ -182,6 +202,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         for (int t = 0; t < FA_TILES; ++t) {
           if (jb < nb[t]) {
             mbar_wait(&p_ready[t], jb & 1, p.status, 304);
+            FA_TRACE(8 + t, jb);
             tc_fence_after();
             issue_pv(t, jb);
           }
@@ -198,9 +219,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
       }
     }
   } else {
-    // ---- softmax warpgroups: thread = one query row of tile t -------------------------------
-    const int t = (warp - 2) >> 2;
-    const int q = warp & 3;  // TMEM lane quadrant this warp may touch
+    // ---- softmax: 8 warps per tile. A thread owns one query row (TMEM lane) and one half of
+    // the block's 128 keys; the two warps of a lane quadrant exchange their row maxima through
+    // shared memory once per block, and their row sums once at the end. ------------------------
+    const int t = (warp - 2) >> 3;
+    const int q = warp & 3;              // TMEM lane quadrant this warp may touch
+    const int hh = ((warp - 2) >> 2) & 1;  // which half of the keys (and of O's columns)
     const int rit = q * 32 + lane;
     const int row = i0 + t * FA_BM + rit;
     const int st = (p.starts && row < p.S) ? p.starts[row] : 0;
@@ -208,29 +232,37 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     const uint32_t tmem_s = tmem + lane_base + t * 128;
     const uint32_t tmem_o = tmem + lane_base + 256 + t * D;
+    float* xch = (float*)(smem + SM::OFF_XCH) + (t * 2) * FA_BM;  // [2 halves][128 rows]
+    const int pair_bar = 1 + t * 4 + q;  // named barrier of this row quadrant's two warps
+    constexpr int HK = FA_BN / 2;        // keys per thread per block
+    constexpr int HD = D / 2;            // O columns per thread
     const int nbt = nb[t];
     float m_ref = -1e30f, l = 0.f;
     for (int jb = 0; jb < nbt; ++jb) {
-      const int key0 = lo + jb * FA_BN;
+      const int key0 = lo + jb * FA_BN + hh * HK;
+      const bool tr = t == 0 && q == 0 && hh == 0 && lane == 0;
+      if (tr) FA_TRACE(0, jb);
       mbar_wait(&s_full[t], jb & 1, p.status, 306);
+      if (tr) FA_TRACE(1, jb);
       // S(j) is ordered behind P V(j-1) on the tensor pipe, so O is quiescent now.
       if (jb > 0) mbar_wait(&o_done[t], (jb - 1) & 1, p.status, 307);
       tc_fence_after();
-      uint32_t sv[FA_BN];
+      uint32_t sv[HK];
 #pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c) tmem_ld32(tmem_s + c * 32, sv + c * 32);
+      for (int c = 0; c < HK / 32; ++c) tmem_ld32(tmem_s + hh * HK + c * 32, sv + c * 32);
       tmem_ld_wait();
+      if (tr) FA_TRACE(2, jb);
       // Keys beyond the diagonal, before the row's own prompt, or past the end are masked.
       // Blocks that lie wholly inside skip the tests. The scale (positive) is applied with the
       // subtraction of the maximum, in one fused multiply-add per score.
-      const bool inside = key0 + FA_BN - 1 <= row && key0 >= st && key0 + FA_BN <= p.S;
+      const bool inside = key0 + HK - 1 <= row && key0 >= st && key0 + HK <= p.S;
       float mx = -INFINITY;
       if (inside) {
 #pragma unroll
-        for (int i = 0; i < FA_BN; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        for (int i = 0; i < HK; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
       } else {
 #pragma unroll
-        for (int i = 0; i < FA_BN; ++i) {
+        for (int i = 0; i < HK; ++i) {
           const int col = key0 + i;
           const bool ok = col <= row && col >= st && col < p.S;
           const float x = ok ? __uint_as_float(sv[i]) : -INFINITY;
@@ -238,55 +270,68 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           mx = fmaxf(mx, x);
         }
       }
-      mx *= sc2;  // log2 domain
+      // Row maximum over both halves (log2 domain).
+      xch[hh * FA_BM + rit] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      mx = fmaxf(mx, xch[(hh ^ 1) * FA_BM + rit]) * sc2;
+      if (tr) FA_TRACE(3, jb);
       const float m_new = fmaxf(m_ref, mx);
-      // Lazy rescale: keep the old reference maximum unless this row outgrew it by 2^8.
+      // Lazy rescale: keep the old reference maximum unless this row outgrew it by 2^8. Both
+      // warps of the row take the same decision from the same numbers.
       const bool grow = m_new > m_ref + RESCALE_STEP;
       if (jb == 0) {
         m_ref = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
         const float f = grow ? exp2f(m_ref - m_new) : 1.0f;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < HD; c0 += 32) {
           uint32_t ov[32];
-          tmem_ld32(tmem_o + c0, ov);
+          tmem_ld32(tmem_o + hh * HD + c0, ov);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
-          tmem_st32(tmem_o + c0, ov);
+          tmem_st32(tmem_o + hh * HD + c0, ov);
         }
-        tmem_st_wait();
         l *= f;
         if (grow) m_ref = m_new;
       }
-      // Probabilities relative to m_ref, rounded to f16 (kernels/llm.tl:143) into tensor memory.
+      // Probabilities relative to m_ref, rounded to f16 (kernels/llm.tl:143) into tensor memory:
+      // keys 2c, 2c+1 of the block share column c of the P region.
       float sum = 0.f;
+      uint32_t pk[HK / 2];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float a = exp2f(fmaf(__uint_as_float(sv[half * 64 + 2 * i]), sc2, -m_ref));
-          const float b = exp2f(fmaf(__uint_as_float(sv[half * 64 + 2 * i + 1]), sc2, -m_ref));
-          sum += a + b;
-          pk[i] = pack_h2(a, b);
-        }
-        tmem_st32(tmem_s + half * 32, pk);
+      for (int i = 0; i < HK / 2; ++i) {
+        const float xa = fmaf(__uint_as_float(sv[2 * i]), sc2, -m_ref);
+        const float xb = fmaf(__uint_as_float(sv[2 * i + 1]), sc2, -m_ref);
+        // (Moving a share of these to an FMA-pipe polynomial was measured and did not help: the
+        // phase is bound by instruction issue, not by the special-function unit.)
+        const float a = exp2_sfu(xa), b = exp2_sfu(xb);
+        sum += a + b;
+        pk[i] = pack_h2(a, b);
       }
+      // The pair barrier above also ordered the other warp's reads of S before this overwrite.
+      if (tr) FA_TRACE(4, jb);
+      tmem_st32(tmem_s + hh * (HK / 2), pk);
       tmem_st_wait();
+      if (tr) FA_TRACE(5, jb);
       l += sum;
       tc_fence_before();
       mbar_arrive(&p_ready[t]);
     }
     if (nbt > 0) {
+      // Row sum over both halves (same reference maximum on both sides).
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      xch[hh * FA_BM + rit] = l;
+      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+      l += xch[(hh ^ 1) * FA_BM + rit];
       mbar_wait(&o_done[t], (nbt - 1) & 1, p.status, 308);
       tc_fence_after();
       const float inv = 1.0f / l;
-      __half* o = p.plain ? p.O + ((size_t)h * p.S + row) * D : p.O + ((size_t)row * p.H + h) * D;
+      __half* o = (p.plain ? p.O + ((size_t)h * p.S + row) * D : p.O + ((size_t)row * p.H + h) * D) + hh * HD;
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t ov[32];
-        tmem_ld32(tmem_o + c0, ov);
+        tmem_ld32(tmem_o + hh * HD + c0, ov);
         tmem_ld_wait();
         if (row < p.S) {
 #pragma unroll
