@@ -79,7 +79,13 @@ int tb200_host_free(tb200_ctx* ctx, void* ptr);
  * (picked[T], tok[T], pos[T], slot[T], lens[T], table[T,MP], hist[S,T], then
  * the i32 scalars n, P and step: the next decode step's inputs for rows < n,
  * computed on the device as src/llm/sched.rs:139-144 computes them on the
- * host, the picks also stored in hist[step]). The
+ * host, the picks also stored in hist[step]); argmax_partial (X f32[M,N],
+ * pairs f32[R,M,2], then the i32 scalars rank and base: with the LM head's rows
+ * split across R ranks, this rank's first maximum over its columns
+ * [base, base+N) as (value, index) in slot `rank`, zeros in the other slots, so
+ * that tb200_allreduce gathers the slots) and argmax_merge (pairs f32[R,M,2],
+ * out i32[M]: the first maximum over the ranks, the token src/llm/mod.rs:132-140
+ * picks from the whole row). The
  * reference's `meta` and `warps` arguments have no equivalent: tile shapes are
  * chosen inside. */
 int tb200_kernel(tb200_ctx* ctx, const char* name, const int64_t* shapes, const int32_t* ranks, int n_arrays,

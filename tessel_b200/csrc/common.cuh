@@ -41,6 +41,8 @@ enum Kind : int {
   K_ROPE_KV,        // rope_q and kv_write in one launch
   K_TP_REDUCE_NORM, // cross-rank sum of partial products + residual add + RMSNorm over peer memory
   K_DECODE_ADVANCE, // next decode step's tok/pos/slot/lens from this step's picks, on the device
+  K_ARGMAX_PARTIAL, // a rank's (maximum, index) over its slice of a vocabulary split across ranks
+  K_ARGMAX_MERGE,   // first maximum over the ranks' parts
   K_COUNT
 };
 

@@ -83,6 +83,8 @@ static const KindInfo KINDS[] = {
     {"decode_advance", K_DECODE_ADVANCE, 7, 10},
     {"tp_reduce_norm", K_TP_REDUCE_NORM, 3, 7},
     {"rope_kv", K_ROPE_KV, 10, 10},
+    {"argmax_partial", K_ARGMAX_PARTIAL, 2, 4},
+    {"argmax_merge", K_ARGMAX_MERGE, 2, 2},
 };
 
 static bool is_gemm(Kind k) {

@@ -7,6 +7,8 @@
 // Rounding follows tessel's interpreter: every f32 product, sum and quotient
 // is rounded on its own (no fused multiply-add), so that the KV pages written
 // here are bit-identical to the reference's CPU path for identical inputs.
+#include <climits>
+
 #include "common.cuh"
 
 namespace tb {
@@ -284,6 +286,85 @@ __global__ void residual_add_kernel(float* __restrict__ R, const float* __restri
   }
 }
 
+// One rank's part of a row maximum over a vocabulary split across ranks: X holds columns
+// [base, base + N) of the full row. Writes (value, global index as f32) to this rank's slot of
+// pairs[R][M][2] and zeros to the other slots, so that a sum over ranks gathers every slot.
+// The value is the first maximum among the columns that are not NaN; a slice with none gives
+// (-inf, -1). Rank 0 reports (NaN, 0) when the row's very first value is NaN, because the
+// sequential scan of src/llm/mod.rs:132-140 never leaves a NaN it starts on.
+__global__ void argmax_partial_kernel(const float* __restrict__ X, float* __restrict__ pairs, int M, int N, int R,
+                                      int rank, int base) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  const int row = blockIdx.x;
+  const float* x = X + (size_t)row * N;
+  float best = -INFINITY;
+  int at = INT_MAX;
+  for (int c = threadIdx.x; c < N; c += blockDim.x) {
+    const float v = x[c];
+    if (v > best || (v == best && c < at)) {
+      best = v;
+      at = c;
+    }
+  }
+  auto merge = [](float& v, int& i, float ov, int oi) {
+    if (ov > v || (ov == v && oi < i)) {
+      v = ov;
+      i = oi;
+    }
+  };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+    merge(best, at, ov, oi);
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) {
+    bv[w] = best;
+    bi[w] = at;
+  }
+  __syncthreads();
+  if (w == 0) {
+    best = (l < nw) ? bv[l] : -INFINITY;
+    at = (l < nw) ? bi[l] : INT_MAX;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+      merge(best, at, ov, oi);
+    }
+    if (l < R) {
+      float2 out = make_float2(0.f, 0.f);
+      if (l == rank) {
+        out = make_float2(best, at == INT_MAX ? -1.0f : (float)(base + at));
+        if (base == 0 && x[0] != x[0]) out = make_float2(x[0], 0.f);
+      }
+      reinterpret_cast<float2*>(pairs)[(size_t)l * M + row] = out;
+    }
+  }
+}
+
+// The row maximum over the ranks' parts, taken in rank order so that the earliest index wins a
+// tie; a NaN first value keeps index 0, as the sequential scan does.
+__global__ void argmax_merge_kernel(const float* __restrict__ pairs, int* __restrict__ out, int M, int R) {
+  pdl_launch();
+  pdl_wait();
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  const float2* p = reinterpret_cast<const float2*>(pairs);
+  float2 best = p[row];
+  if (best.x == best.x) {
+    for (int r = 1; r < R; ++r) {
+      const float2 v = p[(size_t)r * M + row];
+      if (v.y >= 0.f && (v.x > best.x || best.y < 0.f)) best = v;
+    }
+  }
+  out[row] = best.y < 0.f ? 0 : (int)best.y;
+}
+
 // First index of each row's maximum (src/llm/mod.rs:132-140: a later equal
 // value does not replace an earlier one; NaN never wins). One block per row.
 __global__ void argmax_rows_kernel(const float* __restrict__ X, int* __restrict__ out, int N) {
@@ -412,6 +493,15 @@ int make_glue(Ctx* c, Op& op) {
     case K_ARGMAX_ROWS:
       if (s[0].size() != 2 || s[1][0] != s[0][0] || s[0][1] < 1) return bad("shapes are X[M,N], out[M]");
       break;
+    case K_ARGMAX_PARTIAL:
+      if (s[0].size() != 2 || s[1].size() != 3 || s[1][1] != s[0][0] || s[1][2] != 2 || s[0][1] < 1 || s[1][0] < 1 ||
+          s[1][0] > 32)
+        return bad("shapes are X[M,N], pairs[R,M,2] with 1 <= R <= 32");
+      break;
+    case K_ARGMAX_MERGE:
+      if (s[0].size() != 3 || s[0][2] != 2 || s[1].size() != 1 || s[1][0] != s[0][1] || s[0][0] < 1)
+        return bad("shapes are pairs[R,M,2], out[M]");
+      break;
     case K_DECODE_ADVANCE:
       if (s[5].size() != 2 || s[5][0] != s[0][0] || s[6].size() != 2 || s[6][1] != s[0][0])
         return bad("shapes are picked[T], tok[T], pos[T], slot[T], lens[T], table[T,MP], hist[S,T]");
@@ -497,6 +587,21 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
       const int M = (int)s[0][0], N = (int)s[0][1];
       if (M == 0) return 0;
       TB_CUDA(c, launch_k(c, argmax_rows_kernel, dim3(M), dim3(1024), 0, 1, (const float*)a[0], (int*)a[1], N));
+      break;
+    }
+    case K_ARGMAX_PARTIAL: {
+      const int M = (int)s[0][0], N = (int)s[0][1], R = (int)s[1][0];
+      const int rank = (int)(uint32_t)a[2], base = (int)(uint32_t)a[3];
+      if (rank < 0 || rank >= R || base < 0 || (long long)base + N > (1 << 24))
+        return fail(c, "argmax_partial: 0 <= rank < R and base + N <= 2^24 (indices travel as f32)");
+      if (M == 0) return 0;
+      TB_CUDA(c, launch_k(c, argmax_partial_kernel, dim3(M), dim3(1024), 0, 1, (const float*)a[0], (float*)a[1], M, N, R, rank, base));
+      break;
+    }
+    case K_ARGMAX_MERGE: {
+      const int R = (int)s[0][0], M = (int)s[0][1];
+      if (M == 0) return 0;
+      TB_CUDA(c, launch_k(c, argmax_merge_kernel, dim3((M + 127) / 128), dim3(128), 0, 1, (const float*)a[0], (int*)a[1], M, R));
       break;
     }
     case K_DECODE_ADVANCE: {

@@ -48,7 +48,8 @@ class Packed:
 
 @dataclass
 class Decode:
-    """One token per sequence against its cache: page tables and lengths (including the token itself)."""
+    """One token per sequence against its cache: page tables and lengths (including the token itself).
+    ``tables`` is a list of page lists, or an int32 array ``[sequences, pages]`` padded with zeros."""
     tables: Sequence[Sequence[int]]
     lens: Sequence[int]
 
@@ -165,6 +166,15 @@ class Engine:
         self._logits_host: Optional[np.ndarray] = None
         self._hist: Optional[Buf] = None
         self._hist_rows = 0
+        # Greedy steps under tensor parallelism split the LM head's rows (the vocabulary) across the
+        # ranks: each rank reads 1/nranks of the head, finds its own first maximum, and the
+        # (value, index) pairs are gathered by one small allreduce. Logits for ``step`` still come
+        # from the whole head, which every rank keeps (it is the embedding when the two are tied).
+        self.vocab_parallel = nranks > 1 and cfg.vocab % nranks == 0 and cfg.vocab <= 1 << 24
+        if self.vocab_parallel:
+            vs = cfg.vocab // nranks
+            self.head_slice = Buf(self.head.ptr + rank * vs * cfg.dim * 2, vs * cfg.dim * 2)
+            self.pairs = a(nranks * t * 2 * 4)
         self.tp_table: Optional[Buf] = None
         if nranks > 1 and exchange is not None:
             _, fb, eb = gpu.tp_sizes()
@@ -214,10 +224,17 @@ class Engine:
         else:
             tb = st[6 * T:6 * T + t * mp].reshape(t, mp)
             ln = st[4 * T:4 * T + t]
-            tb[:] = 0
             ln[:] = 0
-            for b, row in enumerate(attn.tables):
-                tb[b, :len(row)] = row
+            if isinstance(attn.tables, np.ndarray):
+                # Already padded by the caller (the scheduler keeps it between steps): one copy.
+                rows, cols = attn.tables.shape
+                tb[:rows, :cols] = attn.tables
+                tb[:rows, cols:] = 0
+                tb[rows:] = 0
+            else:
+                tb[:] = 0
+                for b, row in enumerate(attn.tables):
+                    tb[b, :len(row)] = row
             ln[:len(attn.lens)] = attn.lens
             g.write_async(self.table, 0, tb)
             g.write_async(self.lens, 0, ln)
@@ -397,6 +414,15 @@ class Engine:
         fin = k("rmsnorm_rows", [[t, dm], [bw], [dm], [bw, dm]])
         head = k("logits", [[bw, dm], [v, dm], [bw, v]])
         g.launch(fin, [self.x, self.idx, self.norm, self.last, eps])
+        if greedy and self.vocab_parallel:
+            from .gpu import I32
+            r, n = self.rank, self.nranks
+            vs = v // n
+            g.launch(k("logits", [[bw, dm], [vs, dm], [bw, vs]]), [self.last, self.head_slice, self.logits])
+            g.launch(k("argmax_partial", [[bw, vs], [n, bw, 2]]), [self.logits, self.pairs, I32(r), I32(r * vs)])
+            g.allreduce(self.pairs, n * bw * 2, 0)
+            g.launch(k("argmax_merge", [[n, bw, 2], [bw]]), [self.pairs, self.picked])
+            return
         g.launch(head, [self.last, self.head, self.logits])
         if greedy:
             pick = k("argmax_rows", [[bw, v], [bw]])

@@ -70,6 +70,10 @@ class Scheduler:
         self.out = [Output() for _ in reqs]
         self.st = Stats()
         self.max_batch = min(max_batch, e.lim.max_tokens)
+        # The running sequences' block tables as one padded array, rebuilt only when the set of
+        # running sequences changes (pages are reserved for a sequence's whole life).
+        self._table_ids: tuple = ()
+        self._table_np = np.zeros((0, 0), np.int32)
 
     def done(self) -> bool:
         return not self.waiting and not self.running
@@ -106,7 +110,14 @@ class Scheduler:
         toks = [s.last for s in run]
         pos = [s.len for s in run]
         slots = [s.pages[s.len // p] * p + s.len % p for s in run]
-        return toks, pos, slots, Decode([s.pages for s in run], [s.len + 1 for s in run]), list(range(len(run)))
+        ids = tuple(s.id for s in run)
+        if ids != self._table_ids:
+            width = max(len(s.pages) for s in run)
+            tb = np.zeros((len(run), width), np.int32)
+            for b, s in enumerate(run):
+                tb[b, :len(s.pages)] = s.pages
+            self._table_ids, self._table_np = ids, tb
+        return toks, pos, slots, Decode(self._table_np, [s.len + 1 for s in run]), list(range(len(run)))
 
     def absorb(self, picks: Sequence[int]) -> None:
         """Books one decode step's picks: lengths, outputs, finished sequences and their pages."""

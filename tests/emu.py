@@ -140,6 +140,29 @@ class EmuGpu:
         elif name == "argmax_rows":
             x = A(0, f)
             A(1, i)[:] = [oracle.argmax(r) for r in x]
+        elif name == "argmax_partial":
+            x, pr = A(0, f), A(1, f)
+            rank, base = sc(2), sc(3)
+            pr[:] = 0
+            for m, row in enumerate(x):
+                ok = ~np.isnan(row)
+                if base == 0 and not ok[0]:
+                    pr[rank, m] = (np.nan, 0)
+                elif not ok.any():
+                    pr[rank, m] = (-np.inf, -1)
+                else:
+                    at = int(np.argmax(np.where(ok, row, -np.inf)))
+                    pr[rank, m] = (row[at], base + at)
+        elif name == "argmax_merge":
+            pr, out = A(0, f), A(1, i)
+            for m in range(pr.shape[1]):
+                best = pr[0, m]
+                if not np.isnan(best[0]):
+                    for r in range(1, pr.shape[0]):
+                        v = pr[r, m]
+                        if v[1] >= 0 and (v[0] > best[0] or best[1] < 0):
+                            best = v
+                out[m] = 0 if best[1] < 0 else int(best[1])
         else:
             raise GpuError(f"no kernel {name}")
 

@@ -107,6 +107,44 @@ def test_residual_add_and_argmax(gpu):
     assert pick[0] == 17 and pick[1] == 4999 and pick[2] == 0 and pick[3] == 0 and pick[5] == 0
 
 
+@pytest.mark.parametrize("R", [2, 4, 8])
+def test_argmax_over_a_split_vocabulary(gpu, R):
+    """argmax_partial on each of R column slices, the slots summed as the allreduce sums them,
+    then argmax_merge: the token the whole-row scan picks."""
+    from tessel_b200.gpu import I32
+    r = oracle.Rng(6)
+    M, V = 19, 4096
+    vs = V // R
+    x = r.tensor(f, (M, V))
+    x[0, 17] = x[0, V - 3] = 5.0           # a tie across slices: the first wins
+    x[1, V - 1] = 9.0
+    x[2, :] = 1.0                          # all equal: index 0
+    x[3, 100] = np.nan                     # a NaN inside never wins
+    x[4, 0] = np.nan                       # a NaN first sticks
+    x[5, vs] = np.nan                      # a later slice that begins with NaN is still searched
+    x[5, vs + 5] = 7.0
+    x[6, vs:2 * vs] = np.nan               # a slice with nothing to offer
+    x[7, :] = -np.inf
+    x[8, :vs] = -np.inf                    # the first slice offers only -inf
+    total = np.zeros((R, M, 2), f)
+    for rank in range(R):
+        part = np.ascontiguousarray(x[:, rank * vs:(rank + 1) * vs])
+        bufs = [gpu.tensor(part), gpu.tensor(np.full((R, M, 2), 3.0, f))]
+        k = gpu.kernel("argmax_partial", [part.shape, (R, M, 2)])
+        gpu.launch(k, bufs + [I32(rank), I32(rank * vs)])
+        gpu.sync()
+        pr = gpu.fetch(bufs[1], f, (R, M, 2))
+        others = [q for q in range(R) if q != rank]
+        assert not pr[others].any(), "the other ranks' slots must be zero"
+        total += pr
+        for b in bufs:
+            gpu.free(b)
+    (pick,) = run(gpu, "argmax_merge", [total, np.zeros(M, i32)], [1], scalars=())
+    want = np.asarray([oracle.argmax(row) for row in x], i32)
+    assert np.array_equal(pick, want)
+    assert pick[0] == 17 and pick[4] == 0 and pick[5] == vs + 5 and pick[7] == 0
+
+
 def test_argument_checks(gpu):
     from tessel_b200.gpu import GpuError
     with pytest.raises(GpuError, match="no kernel"):
