@@ -102,3 +102,17 @@ def test_graph_replay_equals_plain_launches(gpu):
     e2.graphs = False
     b, _ = generate_with(e2, reqs, 16, False, device_argmax=True)
     assert [o.tokens for o in a] == [o.tokens for o in b]
+
+
+def test_engine_from_a_checkpoint_directory(gpu, tmp_path):
+    """A model saved as a Hugging Face directory and loaded back generates the same tokens as the
+    model it was saved from (src/llm/safetensors.rs:324-443)."""
+    from tessel_b200 import checkpoint
+    cfg = small()
+    w = Weights.random(cfg, 21)
+    checkpoint.save(w, str(tmp_path))
+    lim = Limits(page=16, pages=32, max_tokens=64, max_seq_pages=8)
+    reqs = [Request([1, 5, 9, 200, 31], 8), Request(list(range(40, 70)), 8)]
+    a, _ = generate_with(Engine(gpu, w, lim), reqs, 2, True, device_argmax=True)
+    b, _ = generate_with(Engine(gpu, checkpoint.load(str(tmp_path)), lim), reqs, 2, True, device_argmax=True)
+    assert [o.tokens for o in a] == [o.tokens for o in b]
