@@ -60,6 +60,15 @@ def padded(n: int) -> int:
     return 1 << (n - 1).bit_length()
 
 
+def padded_prefill(n: int) -> int:
+    """Rows a prefill step is made for. The reference pads every step to a power of two because
+    its kernels are compiled per shape; here a prefill step's kernels take ragged row counts and
+    are not replayed as graphs, so beyond 256 rows the step is padded to the next multiple of 256
+    only (a 1300-token step runs 1536 rows, not 2048). Padding rows write to no slot and no
+    wanted row is one of them, so results do not depend on the choice."""
+    return padded(n) if n <= 256 else -(-n // 256) * 256
+
+
 def shard_weights(w: Weights, rank: int, nranks: int) -> Weights:
     """Rank ``rank``'s slice of the model under ``nranks``-way tensor parallelism.
 
@@ -195,7 +204,8 @@ class Engine:
         n = len(tokens)
         if n == 0 or n > self.lim.max_tokens or len(pos) != n or len(slots) != n:
             raise ValueError(f"a step of {n} tokens (at most {self.lim.max_tokens})")
-        t = padded(n)
+        prefill = not isinstance(attn, Decode)
+        t = padded_prefill(n) if prefill else padded(n)
         ns = self.lim.pages * self.lim.page
         mp = self.lim.max_seq_pages
         T = self.tmax
@@ -209,7 +219,6 @@ class Engine:
         g.write_async(self.tok, 0, tk)
         g.write_async(self.pos, 0, ps)
         g.write_async(self.slot, 0, sl)
-        prefill = not isinstance(attn, Decode)
         if prefill:
             # Where each row's sequence begins (padding rows: at themselves).
             sr = st[5 * T:5 * T + t]

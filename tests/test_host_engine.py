@@ -8,7 +8,7 @@ import pytest
 import oracle
 from emu import EmuGpu
 from refs import rel_err
-from tessel_b200.engine import Decode, Engine, Limits, Packed, Prefill, padded, shard_weights
+from tessel_b200.engine import Decode, Engine, Limits, Packed, Prefill, padded, padded_prefill, shard_weights
 from tessel_b200.model import Config, Weights, argmax
 from tessel_b200.sched import Request, generate, generate_with
 
@@ -19,6 +19,24 @@ def limits():
 
 def test_padded():
     assert [padded(n) for n in (1, 16, 17, 32, 33, 300)] == [16, 16, 32, 32, 64, 512]
+
+
+def test_long_prefill_steps_pad_to_256_rows_and_change_nothing():
+    assert [padded_prefill(n) for n in (1, 17, 256, 257, 300, 512, 1300, 2048)] == [16, 32, 256, 512, 512, 512, 1536,
+                                                                                   2048]
+    cfg = Config.tiny()
+    w = Weights.random(cfg, 5)
+    lim = Limits(page=8, pages=128, max_tokens=600, max_seq_pages=80)
+    prompt = [1 + (i * 29 % 250) for i in range(250)]
+    # 250 + 30 tokens in one packed step: 280 rows run as 512; alone, 250 rows run as 256.
+    reqs = [Request(prompt, 3), Request(prompt[:30], 3)]
+    g = EmuGpu()
+    packed, _ = generate_with(Engine(g, w, lim), reqs, 2, True)
+    shapes = {k[1][0] for k in g._kernels if k[0] == "embed"}
+    assert (512,) in shapes
+    single, _ = generate_with(Engine(EmuGpu(), w, lim), reqs, 2, False)
+    for a, b in zip(packed, single):
+        assert a.tokens == b.tokens
 
 
 def test_prefill_and_batched_decode_match_the_reference():
