@@ -283,14 +283,15 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         m_ref = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
         const float f = grow ? exp2f(m_ref - m_new) : 1.0f;
+        // Eight columns at a time: the block's scores stay in registers across this (rare) path.
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t ov[32];
-          tmem_ld32(tmem_o + hh * HD + c0, ov);
+        for (int c0 = 0; c0 < HD; c0 += 8) {
+          uint32_t ov[8];
+          tmem_ld8(tmem_o + hh * HD + c0, ov);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
-          tmem_st32(tmem_o + hh * HD + c0, ov);
+          for (int i = 0; i < 8; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
+          tmem_st8(tmem_o + hh * HD + c0, ov);
         }
         l *= f;
         if (grow) m_ref = m_new;
