@@ -29,7 +29,10 @@ namespace {
 constexpr int FA_BM = 128;        // query rows per tile (one MMA's M)
 constexpr int FA_TILES = 2;       // query tiles per CTA: two softmax warpgroups take turns on the tensor pipe
 constexpr int FA_BN = 128;        // keys per block
-constexpr int FA_THREADS = 576;   // warp 0 TMA, warp 1 MMA, warps 2-9 and 10-17 softmax of tile 0 and 1
+constexpr int FA_THREADS = 640;   // warp 0 TMA, warp 1 MMA, (2, 3 idle), warps 4-11 and 12-19 softmax of tile 0 and 1
+// The first warpgroup gives registers back, the softmax warpgroups take them (setmaxnreg): with
+// five warps per scheduler the even split is 96 registers, too few to keep a block's scores.
+constexpr int FA_REGS_ISSUE = 56, FA_REGS_SOFTMAX = 104;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;  // O is rescaled only when a row's maximum grew by more than 2^8
 
@@ -128,6 +131,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
 
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(FA_REGS_ISSUE));
   if (warp == 0) {
     if (elect_one()) {
       prefetch_tmap(&mapQ);
@@ -218,13 +222,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
         umma_commit(&kv_empty[jb & 1]);  // K(j), V(j) are free once the MMAs issued so far are done
       }
     }
-  } else {
+  } else if (warp >= 4) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FA_REGS_SOFTMAX));
     // ---- softmax: 8 warps per tile. A thread owns one query row (TMEM lane) and one half of
     // the block's 128 keys; the two warps of a lane quadrant exchange their row maxima through
     // shared memory once per block, and their row sums once at the end. ------------------------
-    const int t = (warp - 2) >> 3;
+    const int t = (warp - 4) >> 3;
     const int q = warp & 3;              // TMEM lane quadrant this warp may touch
-    const int hh = ((warp - 2) >> 2) & 1;  // which half of the keys (and of O's columns)
+    const int hh = ((warp - 4) >> 2) & 1;  // which half of the keys (and of O's columns)
     const int rit = q * 32 + lane;
     const int row = i0 + t * FA_BM + rit;
     const int st = (p.starts && row < p.S) ? p.starts[row] : 0;
