@@ -4,17 +4,19 @@
 //   flash_attention    Q/K/V/O [H,S,D]            (kernels/attention.tl:4-24)
 //
 // tcgen05 path (D in {64, 128}): one CTA owns 256 query rows of one head as two 128-row tiles.
-// A producer warp brings both Q tiles once and then 128-key K and V tiles through a two-stage
-// TMA ring. One thread issues the MMAs: S_t = Q_t K^T (M 128, N 128) into tensor memory, and
-// O_t += P_t V (M 128, N D) with P read straight from tensor memory and O accumulated there.
-// Each tile has eight softmax warps: a thread owns one query row and half of the block's keys
-// (the two warps of a row exchange their row maxima through shared memory); it reads S out of
-// tensor memory, applies scale and the causal / sequence-start mask, rounds P to f16 (as
-// kernels/llm.tl:143 does) and stores it over S's first columns. The MMA order S0 S1 | PV0 S0' | PV1 S1' | ... lets
-// one tile's softmax run while the tensor pipe works on the other tile. The running maximum is
-// lazy: O (in tensor memory) is rescaled only when a row's maximum grew by more than 2^8, which
-// leaves P <= 256 and changes no result beyond rounding; the final division by the row sum is
-// exact in the same reference maximum.
+// A producer warp brings both Q tiles once and then 128-key K and V tiles, in the order K0 V0
+// K1 V1 ..., through one ring of TMA slots. Keys are processed 64 at a time ("sub-blocks"): one
+// thread issues S_t(n) = Q_t K(n)^T (M 128, N 64) into one of the tile's two 64-column score
+// buffers in tensor memory, and O_t += P_t(n) V(n) (M 128, N D, K 64) with P read straight from
+// tensor memory and O accumulated there. The two buffers let S_t(n+1) be computed while the
+// tile's softmax warpgroup (one query row per thread) is still working on sub-block n: it reads
+// S out of tensor memory, applies scale and the causal / sequence-start mask, rounds P to f16
+// (as kernels/llm.tl:143 does) and stores it over the first columns of the same buffer, which
+// S_t(n+2) overwrites only behind P_t(n) V(n) on the tensor pipe. So the softmax warps never
+// wait for the tensor pipe in the steady state, and the two tiles fill each other's gaps. The
+// running maximum is lazy: O (in tensor memory) is rescaled only when a row's maximum grew by
+// more than 2^8, which leaves P <= 256 and changes no result beyond rounding; the final
+// division by the row sum is exact in the same reference maximum.
 //
 // The key loop starts at starts[first row of the block] (not tile aligned) and
 // the running maximum starts at -1e30, as the reference's does.
@@ -28,11 +30,11 @@ namespace {
 
 constexpr int FA_BM = 128;        // query rows per tile (one MMA's M)
 constexpr int FA_TILES = 2;       // query tiles per CTA: two softmax warpgroups take turns on the tensor pipe
-constexpr int FA_BN = 128;        // keys per block
-constexpr int FA_THREADS = 640;   // warp 0 TMA, warp 1 MMA, (2, 3 idle), warps 4-11 and 12-19 softmax of tile 0 and 1
-// The first warpgroup gives registers back, the softmax warpgroups take them (setmaxnreg): with
-// five warps per scheduler the even split is 96 registers, too few to keep a block's scores.
-constexpr int FA_REGS_ISSUE = 56, FA_REGS_SOFTMAX = 104;
+constexpr int FA_BN = 128;        // keys per K / V tile in shared memory
+constexpr int FA_SN = 64;         // keys per sub-block: the unit of S, softmax and P V
+constexpr int FA_THREADS = 128 + FA_TILES * 128;  // warp 0 TMA, warp 1 MMA, (2, 3 idle), one softmax warpgroup per tile
+// The first warpgroup gives registers back, the softmax warpgroups take them (setmaxnreg).
+constexpr int FA_REGS_ISSUE = 56, FA_REGS_SOFTMAX = 216;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;  // O is rescaled only when a row's maximum grew by more than 2^8
 
@@ -67,15 +69,17 @@ struct FaSmem {
   static constexpr int SUB = D / 64;
   static constexpr int Q_TILE = FA_BM * D * 2;
   static constexpr int Q_BYTES = FA_TILES * Q_TILE;
-  static constexpr int KV_BYTES = FA_BN * D * 2;  // one K (or V) tile
-  static constexpr int STAGE = 2 * KV_BYTES;
+  static constexpr int KV_BYTES = FA_BN * D * 2;  // one K (or V) tile = one ring slot
   static constexpr int OFF_KV = Q_BYTES;
-  static constexpr int OFF_BAR = OFF_KV + 2 * STAGE;
-  static constexpr int OFF_XCH = OFF_BAR + 16 * 8;  // row maxima / sums exchanged between half-row warps
-  static constexpr int TOTAL = OFF_XCH + FA_TILES * 2 * FA_BM * 4 + 1024;
-  // Tensor memory: S of tile t at columns [128 t, 128 t + 128) (its first 64 columns are
-  // reused for P as packed f16 pairs), O of tile t at [256 + D t, 256 + D t + D).
+  // As many slots as fit (two are pinned by the MMAs in flight, the rest is read-ahead).
+  static constexpr int NSLOT = (226 * 1024 - Q_BYTES) / KV_BYTES > 8 ? 8 : (226 * 1024 - Q_BYTES) / KV_BYTES;
+  static constexpr int OFF_BAR = OFF_KV + NSLOT * KV_BYTES;
+  static constexpr int TOTAL = OFF_BAR + 32 * 8 + 1024;
+  // Tensor memory: tile t's two score buffers at columns [128 t + 64 b, +64), b = 0, 1 (the
+  // first 32 columns of a buffer are reused for P as packed f16 pairs); O of tile t at
+  // [256 + D t, 256 + D t + D).
   static constexpr int TMEM_COLS = 512;
+  static_assert(NSLOT >= 4, "ring too shallow");
 };
 
 template <int D>
@@ -86,16 +90,17 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   pdl_wait();
   using SM = FaSmem<D>;
   constexpr int SUB = SM::SUB;
+  constexpr int NSLOT = SM::NSLOT;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + SM::OFF_BAR);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* s_full = bars + 5;    // [2], per tile
-  uint64_t* p_ready = bars + 7;   // [2]
-  uint64_t* o_done = bars + 9;    // [2]
-  uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+  uint64_t* kv_full = bars + 1;           // [NSLOT]
+  uint64_t* kv_empty = bars + 1 + NSLOT;  // [NSLOT]
+  uint64_t* s_full = bars + 17;           // [tile][buffer]
+  uint64_t* p_ready = bars + 21;          // [tile][buffer]
+  uint64_t* o_done = bars + 25;           // [tile][sub-block parity]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 29);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Late row blocks see the most keys: they are scheduled first so the grid's tail is short.
@@ -103,21 +108,25 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   const int g = p.plain ? h : h / (p.H / p.G);
   // Every row of the CTA starts at or after the start of its first row (prompts are packed in order).
   const int lo = p.starts ? p.starts[i0] : 0;
-  int nb[FA_TILES];
+  // Sub-blocks of 64 keys each tile visits, counted from `lo`.
+  int nsub[FA_TILES];
 #pragma unroll
   for (int t = 0; t < FA_TILES; ++t) {
     const int r0 = i0 + t * FA_BM;
-    nb[t] = r0 < p.S ? (min(r0 + FA_BM, p.S) - lo + FA_BN - 1) / FA_BN : 0;
+    nsub[t] = r0 < p.S ? (min(r0 + FA_BM, p.S) - lo + FA_SN - 1) / FA_SN : 0;
   }
-  const int nbmax = max(nb[0], nb[1]);
+  const int nmax = max(nsub[0], nsub[1]);
+  const int nitems = 2 * ((nmax + 1) / 2);  // K and V tiles of 128 keys: K0 V0 K1 V1 ...
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NSLOT; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 256);
+      mbar_init(&p_ready[i], FA_BM);
       mbar_init(&o_done[i], 1);
     }
     fence_barrier_init();
@@ -148,88 +157,96 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           else
             tma_load_3d(dst, &mapQ, q_full, sub * 64, h, i0 + t * FA_BM);
         }
-      for (int jb = 0; jb < nbmax; ++jb) {
-        const int s = jb & 1, k = jb >> 1;
-        const int key0 = lo + jb * FA_BN;
-        mbar_wait(&kv_empty[s], (k & 1) ^ 1, p.status, 301);
-        mbar_expect_tx(&kv_full[s], SM::STAGE);
-        unsigned char* kd = smem + SM::OFF_KV + s * SM::STAGE;
-        unsigned char* vd = kd + SM::KV_BYTES;
+      for (int i = 0; i < nitems; ++i) {
+        const int s = i % NSLOT, k = i / NSLOT;
+        const int key0 = lo + (i >> 1) * FA_BN;
+        const CUtensorMap* map = (i & 1) ? &mapV : &mapK;
+        if (i >= NSLOT) mbar_wait(&kv_empty[s], (k & 1) ^ 1, p.status, 301);
+        mbar_expect_tx(&kv_full[s], SM::KV_BYTES);
+        unsigned char* dst = smem + SM::OFF_KV + s * SM::KV_BYTES;
 #pragma unroll
         for (int sub = 0; sub < SUB; ++sub) {
-          if (p.plain) {
-            tma_load_3d(kd + sub * (FA_BN * 128), &mapK, &kv_full[s], sub * 64, key0, g);
-            tma_load_3d(vd + sub * (FA_BN * 128), &mapV, &kv_full[s], sub * 64, key0, g);
-          } else {
-            tma_load_3d(kd + sub * (FA_BN * 128), &mapK, &kv_full[s], sub * 64, g, key0);
-            tma_load_3d(vd + sub * (FA_BN * 128), &mapV, &kv_full[s], sub * 64, g, key0);
-          }
+          if (p.plain)
+            tma_load_3d(dst + sub * (FA_BN * 128), map, &kv_full[s], sub * 64, key0, g);
+          else
+            tma_load_3d(dst + sub * (FA_BN * 128), map, &kv_full[s], sub * 64, g, key0);
         }
       }
     }
   } else if (warp == 1) {
     if (elect_one()) {
-      constexpr uint32_t idesc_s = umma_idesc_f16(FA_BM, FA_BN, 0, 0);
+      constexpr uint32_t idesc_s = umma_idesc_f16(FA_BM, FA_SN, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_f16(FA_BM, D, 0, 1);
-      // S_t(j) = Q_t K(j)^T into tensor memory.
-      auto issue_s = [&](int t, int jb) {
+      auto slot_addr = [&](int item) { return smem_u32(smem + SM::OFF_KV + (item % NSLOT) * SM::KV_BYTES); };
+      // Items [0, ready) of the ring have landed.
+      int ready = 0;
+      auto need = [&](int item) {
+        while (ready <= item) {
+          mbar_wait(&kv_full[ready % NSLOT], (ready / NSLOT) & 1, p.status, 303);
+          ++ready;
+        }
+        tc_fence_after();
+      };
+      // S_t(n) = Q_t K(n)^T into score buffer n & 1: keys [64 n, 64 n + 64) are rows 64 (n & 1) ...
+      // of K tile n >> 1.
+      auto issue_s = [&](int t, int n) {
         const uint32_t qa = smem_u32(smem + t * SM::Q_TILE);
-        const uint32_t ka = smem_u32(smem + SM::OFF_KV + (jb & 1) * SM::STAGE);
+        const uint32_t ka = slot_addr(2 * (n >> 1)) + (n & 1) * (FA_SN * 128);
 #pragma unroll
         for (int kd = 0; kd < D / 16; ++kd) {
           const uint32_t off = (kd >> 2) * (FA_BM * 128) + (kd & 3) * 32;
-          umma_f16(tmem + t * 128, umma_desc_sw128(qa + off, 16, 1024), umma_desc_sw128(ka + off, 16, 1024), idesc_s,
-                   kd > 0 ? 1u : 0u);
+          umma_f16(tmem + t * 128 + (n & 1) * FA_SN, umma_desc_sw128(qa + off, 16, 1024),
+                   umma_desc_sw128(ka + off, 16, 1024), idesc_s, kd > 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[t]);
+        umma_commit(&s_full[t * 2 + (n & 1)]);
       };
-      // O_t (+)= P_t V(j): P is read from tensor memory, V is an N-major operand in shared memory.
-      auto issue_pv = [&](int t, int jb) {
-        const uint32_t va = smem_u32(smem + SM::OFF_KV + (jb & 1) * SM::STAGE) + SM::KV_BYTES;
+      // O_t (+)= P_t(n) V(n): P is read from tensor memory, V is an N-major operand in shared memory.
+      auto issue_pv = [&](int t, int n) {
+        const uint32_t va = slot_addr(2 * (n >> 1) + 1);
 #pragma unroll
-        for (int kk = 0; kk < FA_BN / 16; ++kk)
-          umma_f16_ts(tmem + 256 + t * D, tmem + t * 128 + kk * 8, umma_desc_sw128(va + kk * 2048, FA_BN * 128, 1024),
-                      idesc_o, (jb > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&o_done[t]);
+        for (int kk = 0; kk < FA_SN / 16; ++kk)
+          umma_f16_ts(tmem + 256 + t * D, tmem + t * 128 + (n & 1) * FA_SN + kk * 8,
+                      umma_desc_sw128(va + ((n & 1) * (FA_SN / 16) + kk) * 2048, FA_BN * 128, 1024), idesc_o,
+                      (n > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&o_done[t * 2 + (n & 1)]);
       };
       mbar_wait(q_full, 0, p.status, 302);
-      if (nbmax > 0) {
-        mbar_wait(&kv_full[0], 0, p.status, 303);
-        tc_fence_after();
+      if (nmax > 0) {
+        need(0);
 #pragma unroll
-        for (int t = 0; t < FA_TILES; ++t)
-          if (nb[t] > 0) issue_s(t, 0);
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int t = 0; t < FA_TILES; ++t)
+            if (n < nsub[t]) issue_s(t, n);
+        umma_commit(&kv_empty[0]);  // K tile 0 is free once these are done
       }
-      for (int jb = 0; jb < nbmax; ++jb) {
-        bool next_ready = false;
+      for (int n = 0; n < nmax; ++n) {
 #pragma unroll
         for (int t = 0; t < FA_TILES; ++t) {
-          if (jb < nb[t]) {
-            mbar_wait(&p_ready[t], jb & 1, p.status, 304);
-            FA_TRACE(8 + t, jb);
+          if (n < nsub[t]) {
+            mbar_wait(&p_ready[t * 2 + (n & 1)], (n >> 1) & 1, p.status, 304);
+            FA_TRACE(8 + t, n);
             tc_fence_after();
-            issue_pv(t, jb);
+            need(2 * (n >> 1) + 1);
+            issue_pv(t, n);
           }
-          if (jb + 1 < nb[t]) {
-            if (!next_ready) {
-              mbar_wait(&kv_full[(jb + 1) & 1], ((jb + 1) >> 1) & 1, p.status, 305);
-              tc_fence_after();
-              next_ready = true;
-            }
-            issue_s(t, jb + 1);
+          if (n + 2 < nsub[t]) {
+            need(2 * ((n + 2) >> 1));
+            issue_s(t, n + 2);
           }
         }
-        umma_commit(&kv_empty[jb & 1]);  // K(j), V(j) are free once the MMAs issued so far are done
+        if (n & 1) {
+          // Both halves of V tile n >> 1 and of K tile (n >> 1) + 1 have been issued for both tiles.
+          umma_commit(&kv_empty[(n % NSLOT)]);  // item n = 2 (n >> 1) + 1
+          if (n + 1 < nitems) umma_commit(&kv_empty[(n + 1) % NSLOT]);
+        }
       }
     }
   } else if (warp >= 4) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FA_REGS_SOFTMAX));
-    // ---- softmax: 8 warps per tile. A thread owns one query row (TMEM lane) and one half of
-    // the block's 128 keys; the two warps of a lane quadrant exchange their row maxima through
-    // shared memory once per block, and their row sums once at the end. ------------------------
-    const int t = (warp - 4) >> 3;
-    const int q = warp & 3;              // TMEM lane quadrant this warp may touch
-    const int hh = ((warp - 4) >> 2) & 1;  // which half of the keys (and of O's columns)
+    // ---- softmax: one warpgroup per tile, one query row (TMEM lane) per thread ------------------
+    const int t = (warp - 4) >> 2;
+    const int q = warp & 3;  // TMEM lane quadrant this warp may touch
     const int rit = q * 32 + lane;
     const int row = i0 + t * FA_BM + rit;
     const int st = (p.starts && row < p.S) ? p.starts[row] : 0;
@@ -237,37 +254,38 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
     const uint32_t lane_base = (uint32_t)(q * 32) << 16;
     const uint32_t tmem_s = tmem + lane_base + t * 128;
     const uint32_t tmem_o = tmem + lane_base + 256 + t * D;
-    float* xch = (float*)(smem + SM::OFF_XCH) + (t * 2) * FA_BM;  // [2 halves][128 rows]
-    const int pair_bar = 1 + t * 4 + q;  // named barrier of this row quadrant's two warps
-    constexpr int HK = FA_BN / 2;        // keys per thread per block
-    constexpr int HD = D / 2;            // O columns per thread
-    const int nbt = nb[t];
+    const int nt = nsub[t];
     float m_ref = -1e30f, l = 0.f;
-    for (int jb = 0; jb < nbt; ++jb) {
-      const int key0 = lo + jb * FA_BN + hh * HK;
-      const bool tr = t == 0 && q == 0 && hh == 0 && lane == 0;
-      if (tr) FA_TRACE(0, jb);
-      mbar_wait(&s_full[t], jb & 1, p.status, 306);
-      if (tr) FA_TRACE(1, jb);
-      // S(j) is ordered behind P V(j-1) on the tensor pipe, so O is quiescent now.
-      if (jb > 0) mbar_wait(&o_done[t], (jb - 1) & 1, p.status, 307);
+    for (int n = 0; n < nt; ++n) {
+      const int b = n & 1;
+      const int key0 = lo + n * FA_SN;
+      const bool tr = t == 0 && q == 0 && lane == 0;
+      if (tr) FA_TRACE(0, n);
+      mbar_wait(&s_full[t * 2 + b], (n >> 1) & 1, p.status, 306);
+      if (tr) FA_TRACE(1, n);
       tc_fence_after();
-      uint32_t sv[HK];
+      uint32_t sv[FA_SN];
 #pragma unroll
-      for (int c = 0; c < HK / 32; ++c) tmem_ld32(tmem_s + hh * HK + c * 32, sv + c * 32);
+      for (int c = 0; c < FA_SN / 32; ++c) tmem_ld32(tmem_s + b * FA_SN + c * 32, sv + c * 32);
       tmem_ld_wait();
-      if (tr) FA_TRACE(2, jb);
+      if (tr) FA_TRACE(2, n);
       // Keys beyond the diagonal, before the row's own prompt, or past the end are masked.
-      // Blocks that lie wholly inside skip the tests. The scale (positive) is applied with the
-      // subtraction of the maximum, in one fused multiply-add per score.
-      const bool inside = key0 + HK - 1 <= row && key0 >= st && key0 + HK <= p.S;
-      float mx = -INFINITY;
+      // Sub-blocks that lie wholly inside skip the tests. The scale (positive) is applied with
+      // the subtraction of the maximum, in one fused multiply-add per score.
+      const bool inside = key0 + FA_SN - 1 <= row && key0 >= st && key0 + FA_SN <= p.S;
+      float mx;
       if (inside) {
+        // Four independent chains: one chain of dependent maxima would cost its latency 64 times.
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < HK; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        for (int i = 0; i < FA_SN; i += 4)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) m4[u] = fmaxf(m4[u], __uint_as_float(sv[i + u]));
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       } else {
+        mx = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < HK; ++i) {
+        for (int i = 0; i < FA_SN; ++i) {
           const int col = key0 + i;
           const bool ok = col <= row && col >= st && col < p.S;
           const float x = ok ? __uint_as_float(sv[i]) : -INFINITY;
@@ -275,69 +293,66 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
           mx = fmaxf(mx, x);
         }
       }
-      // Row maximum over both halves (log2 domain).
-      xch[hh * FA_BM + rit] = mx;
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      mx = fmaxf(mx, xch[(hh ^ 1) * FA_BM + rit]) * sc2;
-      if (tr) FA_TRACE(3, jb);
+      mx *= sc2;  // log2 domain
+      if (tr) FA_TRACE(3, n);
       const float m_new = fmaxf(m_ref, mx);
-      // Lazy rescale: keep the old reference maximum unless this row outgrew it by 2^8. Both
-      // warps of the row take the same decision from the same numbers.
+      // Lazy rescale: keep the old reference maximum unless this row outgrew it by 2^8.
       const bool grow = m_new > m_ref + RESCALE_STEP;
-      if (jb == 0) {
+      if (n == 0) {
         m_ref = m_new;
       } else if (__any_sync(0xffffffffu, grow)) {
+        // O must be quiescent. S(n), which has completed, was issued behind P V(n-2), so only
+        // P V(n-1) can still be running. Products of even and odd sub-blocks complete separate
+        // barriers, so that at most one phase of a barrier is ever outstanding here and the
+        // parity test is unambiguous.
+        mbar_wait(&o_done[t * 2 + ((n - 1) & 1)], ((n - 1) >> 1) & 1, p.status, 307);
+        tc_fence_after();
         const float f = grow ? exp2f(m_ref - m_new) : 1.0f;
-        // Eight columns at a time: the block's scores stay in registers across this (rare) path.
+        // Eight columns at a time: the sub-block's scores stay in registers across this (rare) path.
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD; c0 += 8) {
+        for (int c0 = 0; c0 < D; c0 += 8) {
           uint32_t ov[8];
-          tmem_ld8(tmem_o + hh * HD + c0, ov);
+          tmem_ld8(tmem_o + c0, ov);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 8; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * f);
-          tmem_st8(tmem_o + hh * HD + c0, ov);
+          tmem_st8(tmem_o + c0, ov);
         }
         l *= f;
         if (grow) m_ref = m_new;
       }
       // Probabilities relative to m_ref, rounded to f16 (kernels/llm.tl:143) into tensor memory:
-      // keys 2c, 2c+1 of the block share column c of the P region.
+      // keys 2c, 2c+1 of the sub-block share column c of the buffer. The thread holds all of its
+      // scores in registers, so overwriting the buffer's first columns loses nothing.
       float sum = 0.f;
-      uint32_t pk[HK / 2];
+      uint32_t pk[FA_SN / 2];
 #pragma unroll
-      for (int i = 0; i < HK / 2; ++i) {
+      for (int i = 0; i < FA_SN / 2; ++i) {
         const float xa = fmaf(__uint_as_float(sv[2 * i]), sc2, -m_ref);
         const float xb = fmaf(__uint_as_float(sv[2 * i + 1]), sc2, -m_ref);
-        // (Moving a share of these to an FMA-pipe polynomial was measured and did not help: the
-        // phase is bound by instruction issue, not by the special-function unit.)
-        const float a = exp2_sfu(xa), b = exp2_sfu(xb);
-        sum += a + b;
-        pk[i] = pack_h2(a, b);
+        const float a = exp2_sfu(xa), b2 = exp2_sfu(xb);
+        sum += a + b2;
+        pk[i] = pack_h2(a, b2);
       }
-      // The pair barrier above also ordered the other warp's reads of S before this overwrite.
-      if (tr) FA_TRACE(4, jb);
-      tmem_st32(tmem_s + hh * (HK / 2), pk);
+      if (tr) FA_TRACE(4, n);
+      tmem_st32(tmem_s + b * FA_SN, pk);
       tmem_st_wait();
-      if (tr) FA_TRACE(5, jb);
+      if (tr) FA_TRACE(5, n);
       l += sum;
       tc_fence_before();
-      mbar_arrive(&p_ready[t]);
+      mbar_arrive(&p_ready[t * 2 + b]);
     }
-    if (nbt > 0) {
-      // Row sum over both halves (same reference maximum on both sides).
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      xch[hh * FA_BM + rit] = l;
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      l += xch[(hh ^ 1) * FA_BM + rit];
-      mbar_wait(&o_done[t], (nbt - 1) & 1, p.status, 308);
+    if (nt > 0) {
+      // The last two products may still be running (see above).
+      if (nt > 1) mbar_wait(&o_done[t * 2 + ((nt - 2) & 1)], ((nt - 2) >> 1) & 1, p.status, 308);
+      mbar_wait(&o_done[t * 2 + ((nt - 1) & 1)], ((nt - 1) >> 1) & 1, p.status, 309);
       tc_fence_after();
       const float inv = 1.0f / l;
-      __half* o = (p.plain ? p.O + ((size_t)h * p.S + row) * D : p.O + ((size_t)row * p.H + h) * D) + hh * HD;
+      __half* o = p.plain ? p.O + ((size_t)h * p.S + row) * D : p.O + ((size_t)row * p.H + h) * D;
 #pragma unroll 1
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = 0; c0 < D; c0 += 32) {
         uint32_t ov[32];
-        tmem_ld32(tmem_o + hh * HD + c0, ov);
+        tmem_ld32(tmem_o + c0, ov);
         tmem_ld_wait();
         if (row < p.S) {
 #pragma unroll
