@@ -1,24 +1,33 @@
 // Tensor-parallel exchange fused with the residual add and the next RMSNorm.
 //
 // Under tensor parallelism o_proj and down_proj leave, on every rank, an f32 partial product
-// part[T, dim] whose sum over ranks must be added to the residual stream x (replicated on every
-// rank) and then normalised into h for the next projection. The plain path does that with four
-// launches: linear_f32, an NCCL allreduce, residual_add, rmsnorm. `tp_reduce_norm` does the last
-// three in ONE kernel over peer memory (buffers of the other ranks mapped through CUDA IPC and
-// reached over NVLink with ordinary loads and stores; no multicast, no TMA):
+// part[T, dim] whose sum over ranks must be added to the residual stream x and then normalised
+// into h for the next projection. The plain path does that with four launches: linear_f32, an
+// NCCL allreduce, residual_add, rmsnorm. `tp_reduce_norm` does the last three in ONE kernel over
+// peer memory (buffers of the other ranks mapped through CUDA IPC and reached over NVLink with
+// ordinary loads; no multicast, no TMA, and no stores into a peer's memory other than flags):
 //
 //   1. every CTA tells the same-numbered CTA of every peer that this rank's partial is
 //      complete (the kernel runs behind the rank's GEMM on the same stream) and waits for theirs;
-//   2. the row r of the step belongs to rank r % n: its owner loads that row of all n partials
+//   2. row r of the step belongs to rank r % n: its owner loads that row of all n partials
 //      (peers' over NVLink), adds them in rank order to its x row, normalises, and stores the
-//      new x row and h row into EVERY rank's x and h (reduce-scatter and all-gather in one pass,
-//      so each value crosses NVLink once in and once out);
-//   3. every CTA tells its peers that its rows are out, and waits for theirs, so that when the
-//      kernel ends on a rank all of that rank's x and h rows have arrived.
+//      new x row and h row in ITS OWN memory (the reduce-scatter);
+//   3. every CTA tells its peers that its rows are ready, waits for theirs, and copies the other
+//      owners' h rows from their memory into its own h (the all-gather, pulled: a pushed copy
+//      would need a system-wide fence that waits for every remote store to be acknowledged,
+//      measured at 6-9 us per call).
+//
+// Between layers only h is gathered: the residual stream stays distributed (a rank's x is
+// current in the rows it owns), because nothing but this kernel reads it. The last call of a
+// step (do_norm = 0) gathers x instead, for the final norm and the LM head.
 //
 // Sums are taken in rank order by one owner, so x and h are bit-identical on all ranks, which
-// keeps the replicated LM heads (and the greedy tokens) in lockstep. Flag waits are bounded:
-// on time-out the kernel raises the context's status word and returns.
+// keeps the ranks' greedy tokens in lockstep. Flag waits are bounded: on time-out the kernel
+// raises the context's status word and returns.
+//
+// Why the buffers can be reused without a closing barrier: a rank overwrites its partial, or
+// its own x / h rows, only after step 1 of a later call, i.e. after every peer has begun that
+// call and therefore finished reading in this one.
 #include "common.cuh"
 
 namespace tb {
@@ -48,12 +57,36 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   return v;
 }
 
+__device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Loads that always go to the owner's L2 (never a stale line of this SM's L1).
+__device__ __forceinline__ float4 ld_sys_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint2 ld_sys_u2(const void* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 // Thread `tid` < nranks signals peer `tid` and waits for peer `tid`'s signal of this epoch.
+// `release`: the signal publishes stores of this CTA (made before the preceding __syncthreads);
+// without it the signal only says that the previous kernel of this stream has completed.
 __device__ __forceinline__ void exchange_flags(const TpTable& tb_, int slot, int phase, unsigned int epoch,
-                                               unsigned int* status, unsigned int code) {
+                                               bool release, unsigned int* status, unsigned int code) {
   const int tid = threadIdx.x;
   if (tid < tb_.nranks && tid != tb_.rank) {
-    st_release_sys(tb_.flags[tid] + ((size_t)slot * 2 + phase) * TP_MAX + tb_.rank, epoch);
+    unsigned int* theirs = tb_.flags[tid] + ((size_t)slot * 2 + phase) * TP_MAX + tb_.rank;
+    if (release)
+      st_release_sys(theirs, epoch);
+    else
+      st_relaxed_sys(theirs, epoch);
     const unsigned int* mine = tb_.flags[tb_.rank] + ((size_t)slot * 2 + phase) * TP_MAX + tid;
     const unsigned long long t0 = globaltimer();
     unsigned int spins = 0;
@@ -79,17 +112,21 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
   __shared__ TpTable tb_;
   __shared__ float red[32];
   __shared__ unsigned int s_epoch;
-  if (threadIdx.x == 0) {
-    tb_ = *table;
-    s_epoch = tb_.epoch[blockIdx.x] + 1;
-  }
+  static_assert(sizeof(TpTable) % 8 == 0, "the table is copied in 8-byte words");
+  if (threadIdx.x < sizeof(TpTable) / 8)
+    reinterpret_cast<unsigned long long*>(&tb_)[threadIdx.x] =
+        reinterpret_cast<const unsigned long long*>(table)[threadIdx.x];
+  __syncthreads();
+  if (threadIdx.x == 0) s_epoch = tb_.epoch[blockIdx.x] + 1;
   __syncthreads();
   const unsigned int epoch = s_epoch;
   const int n = tb_.nranks, rank = tb_.rank;
-  __threadfence_system();
-  exchange_flags(tb_, blockIdx.x, 0, epoch, status, 401);
+  // 1. The partials were written by the previous kernel of each rank's stream, which has
+  // completed (and flushed to that rank's L2, where peers read them) before this one signals.
+  exchange_flags(tb_, blockIdx.x, 0, epoch, false, status, 401);
   __syncthreads();
 
+  // 2. This rank's rows.
   for (int row = blockIdx.x * n + rank; row < T; row += gridDim.x * n) {
     float4 acc[PER];
     float ss = 0.f;
@@ -101,7 +138,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
         float4 part[TP_MAX];
 #pragma unroll
         for (int r = 0; r < TP_MAX; ++r)
-          if (r < n) part[r] = *reinterpret_cast<const float4*>(tb_.part[which][r] + o);
+          if (r < n) part[r] = ld_sys_f4(tb_.part[which][r] + o);
         float4 s = part[0];
 #pragma unroll
         for (int r = 1; r < TP_MAX; ++r)
@@ -117,9 +154,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
         x.z = __fadd_rn(x.z, s.z);
         x.w = __fadd_rn(x.w, s.w);
         acc[i] = x;
-#pragma unroll
-        for (int r = 0; r < TP_MAX; ++r)
-          if (r < n) *reinterpret_cast<float4*>(tb_.x[r] + o) = x;
+        *reinterpret_cast<float4*>(tb_.x[rank] + o) = x;
         ss += __fmul_rn(x.x, x.x);
         ss += __fmul_rn(x.y, x.y);
         ss += __fmul_rn(x.z, x.z);
@@ -149,18 +184,43 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
                         __fmul_rn(__fmul_rn(acc[i].y, rs), __high2float(w01)));
           y.y = pack_h2(__fmul_rn(__fmul_rn(acc[i].z, rs), __low2float(w23)),
                         __fmul_rn(__fmul_rn(acc[i].w, rs), __high2float(w23)));
-          const size_t o = (size_t)row * dim + c;
-#pragma unroll
-          for (int r = 0; r < TP_MAX; ++r)
-            if (r < n) *reinterpret_cast<uint2*>(tb_.h[r] + o) = y;
+          *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)row * dim + c) = y;
         }
       }
     }
   }
-  __threadfence_system();
+  // 3. Publish this CTA's rows (the release orders the CTA's stores, made before the barrier,
+  // ahead of the flag), wait for the other owners, and copy their rows.
   __syncthreads();
-  exchange_flags(tb_, blockIdx.x, 1, epoch, status, 402);
+  exchange_flags(tb_, blockIdx.x, 1, epoch, true, status, 402);
   __syncthreads();
+  for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int c = (threadIdx.x + i * TP_THREADS) * 4;
+      if (c < dim) {
+        if (do_norm) {
+          uint2 v[TP_MAX];
+#pragma unroll
+          for (int r = 0; r < TP_MAX; ++r)
+            if (r < n && r != rank && base + r < T) v[r] = ld_sys_u2(tb_.h[r] + (size_t)(base + r) * dim + c);
+#pragma unroll
+          for (int r = 0; r < TP_MAX; ++r)
+            if (r < n && r != rank && base + r < T)
+              *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)(base + r) * dim + c) = v[r];
+        } else {
+          float4 v[TP_MAX];
+#pragma unroll
+          for (int r = 0; r < TP_MAX; ++r)
+            if (r < n && r != rank && base + r < T) v[r] = ld_sys_f4(tb_.x[r] + (size_t)(base + r) * dim + c);
+#pragma unroll
+          for (int r = 0; r < TP_MAX; ++r)
+            if (r < n && r != rank && base + r < T)
+              *reinterpret_cast<float4*>(tb_.x[rank] + (size_t)(base + r) * dim + c) = v[r];
+        }
+      }
+    }
+  }
   if (threadIdx.x == 0) tb_.epoch[blockIdx.x] = epoch;
 }
 
