@@ -103,6 +103,19 @@ __device__ __forceinline__ void exchange_flags(const TpTable& tb_, int slot, int
   }
 }
 
+#ifdef TB200_TRACE
+// Development builds: %globaltimer stamps of CTA 0's thread 0 in the unused tail of this rank's flag buffer.
+#define TP_TRACE(k)                                                                                      \
+  do {                                                                                                   \
+    if (blockIdx.x == 0 && threadIdx.x == 0)                                                             \
+      reinterpret_cast<unsigned long long*>(tb_.flags[tb_.rank] + (size_t)(TP_SLOTS - 64) * 2 * TP_MAX)[k] = globaltimer(); \
+  } while (0)
+#else
+#define TP_TRACE(k) \
+  do {              \
+  } while (0)
+#endif
+
 template <int PER>  // float4 chunks per thread: dim <= PER * 4096
 __global__ void __launch_bounds__(TP_THREADS, 1)
     tp_reduce_norm_kernel(const TpTable* __restrict__ table, const __half* __restrict__ W, float eps, int T, int dim,
@@ -121,10 +134,12 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
   __syncthreads();
   const unsigned int epoch = s_epoch;
   const int n = tb_.nranks, rank = tb_.rank;
+  TP_TRACE(0);
   // 1. The partials were written by the previous kernel of each rank's stream, which has
   // completed (and flushed to that rank's L2, where peers read them) before this one signals.
   exchange_flags(tb_, blockIdx.x, 0, epoch, false, status, 401);
   __syncthreads();
+  TP_TRACE(1);
 
   // 2. This rank's rows.
   for (int row = blockIdx.x * n + rank; row < T; row += gridDim.x * n) {
@@ -192,8 +207,10 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
   // 3. Publish this CTA's rows (the release orders the CTA's stores, made before the barrier,
   // ahead of the flag), wait for the other owners, and copy their rows.
   __syncthreads();
+  TP_TRACE(2);
   exchange_flags(tb_, blockIdx.x, 1, epoch, true, status, 402);
   __syncthreads();
+  TP_TRACE(3);
   for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
@@ -221,6 +238,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
       }
     }
   }
+  TP_TRACE(4);
   if (threadIdx.x == 0) tb_.epoch[blockIdx.x] = epoch;
 }
 
