@@ -135,23 +135,28 @@ int tb200_allreduce(tb200_ctx* ctx, uint64_t dptr, size_t count, int dtype);
 /* No counterpart in the reference: the cross-rank sum fused with the residual add
  * and the next RMSNorm, over peer memory (NVLink loads and stores) instead of an
  * NCCL call. Each rank allocates two partial-product buffers f32[T,dim], its
- * residual stream x f32[T,dim], h f16[T,dim], a flag area and an epoch area
- * (tb200_tp_sizes; both zero-filled, as tb200_alloc leaves them), exports them
+ * residual stream x f32[T,dim], h f16[T,dim], a staging buffer of T*dim*4 bytes
+ * (its own h rows interleaved with a per-call counter, from which the peers
+ * copy them), a flag area and an epoch area (tb200_tp_sizes; staging, flags and
+ * epochs zero-filled, as tb200_alloc leaves them), exports them
  * with tb200_ipc_export (a 64-byte handle each), the host hands every rank the
  * others' handles, tb200_ipc_import maps them, and tb200_tp_table writes the
  * table (pointer arrays indexed by rank; a rank's own entries are its local
  * pointers) that the host then uploads to device memory. The kernel
  * "tp_reduce_norm" (arrays: table u8[bytes], W f16[dim], X f32[T,dim]; then
  * eps f32, which i32 = the partial buffer to sum, do_norm i32, nranks i32) adds
- * the ranks' partials in rank order to x, normalises into h (if do_norm), and
- * leaves x and h identical on every rank. Every rank must launch it the same
- * number of times with the same shapes. */
+ * the ranks' partials in rank order to x and, if do_norm, normalises into h and
+ * leaves h identical on every rank (x is then current only in the rows r with
+ * r % nranks == rank); with do_norm = 0 it leaves x identical on every rank
+ * instead. Every rank must launch it the same number of times with the same
+ * shapes. */
 #define TB200_IPC_HANDLE_BYTES 64
 int tb200_ipc_export(tb200_ctx* ctx, uint64_t dptr, void* handle);
 int tb200_ipc_import(tb200_ctx* ctx, const void* handle, uint64_t* dptr);
 int tb200_tp_sizes(size_t* table_bytes, size_t* flag_bytes, size_t* epoch_bytes);
 int tb200_tp_table(tb200_ctx* ctx, void* host_out, size_t bytes, int rank, int nranks, const uint64_t* part0,
-                   const uint64_t* part1, const uint64_t* x, const uint64_t* h, const uint64_t* flags, uint64_t epoch);
+                   const uint64_t* part1, const uint64_t* x, const uint64_t* h, const uint64_t* stage,
+                   const uint64_t* flags, uint64_t epoch);
 
 /* No counterpart in the reference. Paged decode attention (the computation of
  * the "decode_attention" kernel above) for callers that cannot allocate device

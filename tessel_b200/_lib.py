@@ -43,7 +43,7 @@ SYMBOLS = [
     ("tb200_ipc_import", C.c_int, [C.c_void_p, C.c_void_p, _u64p]),
     ("tb200_tp_sizes", C.c_int, [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     ("tb200_tp_table", C.c_int,
-     [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, _u64p, _u64p, _u64p, _u64p, _u64p, C.c_uint64]),
+     [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, _u64p, _u64p, _u64p, _u64p, _u64p, _u64p, C.c_uint64]),
     ("tb200_decode_attention_static", C.c_int,
      [C.c_void_p, C.POINTER(C.c_int32), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
       C.c_float]),

@@ -116,7 +116,7 @@ size_t tp_table_bytes();
 size_t tp_flag_bytes();
 size_t tp_epoch_bytes();
 int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint64_t* part0, const uint64_t* part1,
-                  const uint64_t* x, const uint64_t* h, const uint64_t* flags, uint64_t epoch);
+                  const uint64_t* x, const uint64_t* h, const uint64_t* stage, const uint64_t* flags, uint64_t epoch);
 int launch_prefill(Ctx* c, Op& op, const uint64_t* a);
 
 // Launches `kern` on the context's stream, as a cluster of (1, 1, cluster_z) when cluster_z > 1.

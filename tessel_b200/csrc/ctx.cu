@@ -522,10 +522,10 @@ int tb200_tp_sizes(size_t* table_bytes, size_t* flag_bytes, size_t* epoch_bytes)
 }
 
 int tb200_tp_table(tb200_ctx* h, void* out, size_t bytes, int rank, int nranks, const uint64_t* part0,
-                   const uint64_t* part1, const uint64_t* x, const uint64_t* hh, const uint64_t* flags,
-                   uint64_t epoch) {
+                   const uint64_t* part1, const uint64_t* x, const uint64_t* hh, const uint64_t* stage,
+                   const uint64_t* flags, uint64_t epoch) {
   Ctx* c = &h->c;
-  if (tp_fill_table(out, bytes, rank, nranks, part0, part1, x, hh, flags, epoch))
+  if (tp_fill_table(out, bytes, rank, nranks, part0, part1, x, hh, stage, flags, epoch))
     return fail(c, "tb200_tp_table: 1 to 8 ranks, rank inside, and a buffer of tb200_tp_sizes' table size");
   return 0;
 }

@@ -12,14 +12,17 @@
 //   2. row r of the step belongs to rank r % n: its owner loads that row of all n partials
 //      (peers' over NVLink), adds them in rank order to its x row, normalises, and stores the
 //      new x row and h row in ITS OWN memory (the reduce-scatter);
-//   3. every CTA tells its peers that its rows are ready, waits for theirs, and copies the other
-//      owners' h rows from their memory into its own h (the all-gather, pulled: a pushed copy
-//      would need a system-wide fence that waits for every remote store to be acknowledged,
-//      measured at 6-9 us per call).
+//   3. every CTA copies the other owners' h rows from their memory into its own h (the
+//      all-gather, pulled: a pushed copy would need a system-wide fence that waits for every
+//      remote store to be acknowledged, measured at 6-9 us per call). The owner publishes a row
+//      in a staging buffer whose every 8 bytes hold two halves and the call's epoch, written
+//      and read as units, so a reader knows from the data itself whether it is current and
+//      polls the row directly: no "rows are ready" flag, no release fence.
 //
 // Between layers only h is gathered: the residual stream stays distributed (a rank's x is
 // current in the rows it owns), because nothing but this kernel reads it. The last call of a
-// step (do_norm = 0) gathers x instead, for the final norm and the LM head.
+// step (do_norm = 0) gathers x instead, for the final norm and the LM head, behind a second
+// flag exchange ("my rows are ready", a release).
 //
 // Sums are taken in rank order by one owner, so x and h are bit-identical on all ranks, which
 // keeps the ranks' greedy tokens in lockstep. Flag waits are bounded: on time-out the kernel
@@ -43,6 +46,7 @@ struct TpTable {
   float* part[2][TP_MAX];   // the two partial-product buffers of every rank
   float* x[TP_MAX];         // residual stream of every rank
   __half* h[TP_MAX];        // normalised activations of every rank
+  uint4* stage[TP_MAX];     // [T, dim/4]: a rank's own h rows as {2 halves, epoch, 2 halves, epoch}
   unsigned int* flags[TP_MAX];  // [TP_SLOTS][2 phases][TP_MAX senders]
   unsigned int* epoch;      // [TP_SLOTS], local: launches this slot has taken part in
   int rank, nranks;
@@ -69,9 +73,12 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* p) {
                : "memory");
   return v;
 }
-__device__ __forceinline__ uint2 ld_sys_u2(const void* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_sys_u4(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
   return v;
 }
 
@@ -200,32 +207,67 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
           y.y = pack_h2(__fmul_rn(__fmul_rn(acc[i].z, rs), __low2float(w23)),
                         __fmul_rn(__fmul_rn(acc[i].w, rs), __high2float(w23)));
           *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)row * dim + c) = y;
+          // Each 8-byte half of this store is one unit for a reader (payload and its epoch).
+          tb_.stage[rank][((size_t)row * dim + c) >> 2] = make_uint4(y.x, epoch, y.y, epoch);
         }
       }
     }
   }
-  // 3. Publish this CTA's rows (the release orders the CTA's stores, made before the barrier,
-  // ahead of the flag), wait for the other owners, and copy their rows.
-  __syncthreads();
   TP_TRACE(2);
-  exchange_flags(tb_, blockIdx.x, 1, epoch, true, status, 402);
-  __syncthreads();
-  TP_TRACE(3);
-  for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
+  if (do_norm) {
+    // 3a. The other owners' h rows, polled until both halves of a 16-byte unit carry this epoch.
+    for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const int c = (threadIdx.x + i * TP_THREADS) * 4;
-      if (c < dim) {
-        if (do_norm) {
-          uint2 v[TP_MAX];
+      for (int i = 0; i < PER; ++i) {
+        const int c = (threadIdx.x + i * TP_THREADS) * 4;
+        if (c < dim) {
+          uint4 v[TP_MAX];
+          unsigned int pending = 0;
 #pragma unroll
           for (int r = 0; r < TP_MAX; ++r)
-            if (r < n && r != rank && base + r < T) v[r] = ld_sys_u2(tb_.h[r] + (size_t)(base + r) * dim + c);
+            if (r < n && r != rank && base + r < T) {
+              v[r] = ld_sys_u4(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
+              if (v[r].y != epoch || v[r].w != epoch) pending |= 1u << r;
+            }
+          if (pending) {
+            const unsigned long long t0 = globaltimer();
+            unsigned int spins = 0;
+            while (pending) {
+#pragma unroll
+              for (int r = 0; r < TP_MAX; ++r)
+                if (pending & (1u << r)) {
+                  v[r] = ld_sys_u4(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
+                  if (v[r].y == epoch && v[r].w == epoch) pending &= ~(1u << r);
+                }
+              if ((++spins & 63u) == 0) {
+                if (*(volatile unsigned int*)status != 0) break;
+                if (globaltimer() - t0 > WAIT_LIMIT_NS / 2) {
+                  atomicCAS(status, 0u, 402u);
+                  break;
+                }
+              }
+            }
+          }
 #pragma unroll
           for (int r = 0; r < TP_MAX; ++r)
             if (r < n && r != rank && base + r < T)
-              *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)(base + r) * dim + c) = v[r];
-        } else {
+              *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)(base + r) * dim + c) = make_uint2(v[r].x, v[r].z);
+        }
+      }
+    }
+    TP_TRACE(3);
+  } else {
+    // 3b. Publish this CTA's x rows (the release orders the CTA's stores, made before the
+    // barrier, ahead of the flag), wait for the other owners, and copy their rows.
+    __syncthreads();
+    exchange_flags(tb_, blockIdx.x, 1, epoch, true, status, 403);
+    __syncthreads();
+    TP_TRACE(3);
+    for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const int c = (threadIdx.x + i * TP_THREADS) * 4;
+        if (c < dim) {
           float4 v[TP_MAX];
 #pragma unroll
           for (int r = 0; r < TP_MAX; ++r)
@@ -287,7 +329,7 @@ size_t tp_epoch_bytes() { return (size_t)TP_SLOTS * sizeof(unsigned int); }
 
 // Fills a host copy of the table. Pointer arrays are indexed by rank.
 int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint64_t* part0, const uint64_t* part1,
-                  const uint64_t* x, const uint64_t* h, const uint64_t* flags, uint64_t epoch) {
+                  const uint64_t* x, const uint64_t* h, const uint64_t* stage, const uint64_t* flags, uint64_t epoch) {
   if (out_bytes < sizeof(TpTable) || nranks < 1 || nranks > TP_MAX || rank < 0 || rank >= nranks) return 1;
   TpTable t;
   memset(&t, 0, sizeof t);
@@ -296,6 +338,7 @@ int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint6
     t.part[1][r] = (float*)part1[r];
     t.x[r] = (float*)x[r];
     t.h[r] = (__half*)h[r];
+    t.stage[r] = (uint4*)stage[r];
     t.flags[r] = (unsigned int*)flags[r];
   }
   t.epoch = (unsigned int*)epoch;

@@ -188,14 +188,15 @@ class Engine:
         if nranks > 1 and exchange is not None:
             _, fb, eb = gpu.tp_sizes()
             self.part2 = a(t * cfg.dim * 4)
+            self.tp_stage = a(t * cfg.dim * 4)  # this rank's h rows, tagged with the call's epoch, for the peers
             self.tp_flags, self.tp_epoch = a(fb), a(eb)
-            mine = [self.part, self.part2, self.x, self.h, self.tp_flags]
+            mine = [self.part, self.part2, self.x, self.h, self.tp_stage, self.tp_flags]
             everyone = exchange([gpu.ipc_export(b) for b in mine])
-            cols = [[], [], [], [], []]
+            cols = [[] for _ in mine]
             for r in range(nranks):
                 for i, b in enumerate(mine):
                     cols[i].append(b if r == rank else gpu.ipc_import(everyone[r][i], b.bytes))
-            raw = gpu.tp_table(rank, nranks, cols[0], cols[1], cols[2], cols[3], cols[4], self.tp_epoch)
+            raw = gpu.tp_table(rank, nranks, cols[0], cols[1], cols[2], cols[3], cols[4], cols[5], self.tp_epoch)
             self.tp_table = gpu.tensor(np.frombuffer(raw, np.uint8).copy())
 
     # -- one step ----------------------------------------------------------------

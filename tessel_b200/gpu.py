@@ -266,13 +266,13 @@ class Gpu:
         self._check(self._l.tb200_tp_sizes(C.byref(a), C.byref(b), C.byref(c)))
         return a.value, b.value, c.value
 
-    def tp_table(self, rank: int, nranks: int, part0, part1, x, h, flags, epoch: Buf) -> bytes:
+    def tp_table(self, rank: int, nranks: int, part0, part1, x, h, stage, flags, epoch: Buf) -> bytes:
         """The table ``tp_reduce_norm`` reads: lists of Buf indexed by rank."""
         n = self.tp_sizes()[0]
         out = C.create_string_buffer(n)
         arr = lambda bs: (C.c_uint64 * 8)(*[b.ptr for b in bs])
         self._check(self._l.tb200_tp_table(self._h, out, n, rank, nranks, arr(part0), arr(part1), arr(x), arr(h),
-                                           arr(flags), epoch.ptr))
+                                           arr(stage), arr(flags), epoch.ptr))
         return out.raw
 
     def allreduce(self, b: Buf, count: int, dtype: int = 0) -> None:
