@@ -37,10 +37,6 @@ struct DecodeParams {
   __half* O;
   float* part_acc;  // [B, H, nsplit, D]
   float* part_ml;   // [B, H, nsplit, 2]
-  // [B, kv heads x head groups], zero between launches: splits of a (sequence, head group) that
-  // have stored their partials. The split that completes the count merges them. Null: the
-  // partials are merged by decode_combine_kernel instead.
-  unsigned int* counters;
   float scale;
   int B, H, G, NP, MP, chunk, nsplit;
   unsigned int* status;
@@ -100,7 +96,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
   const int first = split * p.chunk;
   if (n <= 0) {
     // No cached token: the reference's 0/0 (kernels/llm.tl:172 with l == 0).
-    if (split == 0 && p.counters) {
+    if (p.nsplit == 1) {
       const int hq0 = p.H / p.G, hb = g * hq0 + hg * 8, nhb = min(8, hq0 - hg * 8);
       for (int i = threadIdx.x; i < nhb * D; i += blockDim.x)
         p.O[((size_t)b * p.H + hb + i / D) * D + i % D] = __float2half_rn(__int_as_float(0x7fc00000));
@@ -109,7 +105,6 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
   }
   if (first >= npages) return;  // uniform for the CTA: nothing to do
   const int count = min(p.chunk, npages - first);
-  const int ns = (npages + p.chunk - 1) / p.chunk;  // splits of this sequence that have work
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -278,8 +273,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
       lt += base[w * (8 * D + 16) + 8 * D + 8 + hh] * wgt;
       at += base[w * (8 * D + 16) + hh * D + d] * wgt;
     }
-    if (p.counters && ns == 1) {
-      // The only split: no partial to merge.
+    if (p.nsplit == 1) {
+      // The launch has one split per sequence: no partial to merge, no second kernel.
       p.O[((size_t)b * p.H + h0 + hh) * D + d] = __float2half_rn(at / lt);
       continue;
     }
@@ -289,36 +284,6 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
       p.part_ml[o * 2] = mt;
       p.part_ml[o * 2 + 1] = lt;
     }
-  }
-  if (!p.counters || ns == 1) return;
-  // ---- the split that arrives last merges the partials of its (sequence, head group):
-  // O = f16(sum_s acc_s w_s / sum_s l_s w_s), w_s = 2^(m_s - max m).
-  __shared__ int s_last;
-  __threadfence();
-  asm volatile("bar.sync 1, %0;" ::"r"(DEC_WARPS * 32) : "memory");
-  if (threadIdx.x == 0) {
-    unsigned int* cnt = p.counters + (size_t)b * gridDim.y + blockIdx.y;
-    const unsigned int old = atomicAdd(cnt, 1u);
-    s_last = old == (unsigned int)(ns - 1);
-    if (s_last) *cnt = 0;  // every split has arrived: ready for the next launch
-  }
-  asm volatile("bar.sync 1, %0;" ::"r"(DEC_WARPS * 32) : "memory");
-  if (!s_last) return;
-  __threadfence();
-  for (int i = threadIdx.x; i < nh * D; i += DEC_WARPS * 32) {
-    const int hh = i / D, d = i % D;
-    const size_t bh = (size_t)b * p.H + h0 + hh;
-    const float* ml = p.part_ml + bh * p.nsplit * 2;
-    const float* acc = p.part_acc + bh * p.nsplit * D + d;
-    float mt = -INFINITY;
-    for (int s2 = 0; s2 < ns; ++s2) mt = fmaxf(mt, __ldcg(ml + s2 * 2));
-    float lt = 0.f, at = 0.f;
-    for (int s2 = 0; s2 < ns; ++s2) {
-      const float w = exp2f(__ldcg(ml + s2 * 2) - mt);
-      lt += __ldcg(ml + s2 * 2 + 1) * w;
-      at += __ldcg(acc + (size_t)s2 * D) * w;
-    }
-    p.O[bh * D + d] = __float2half_rn(at / lt);
   }
 }
 
@@ -459,11 +424,8 @@ int make_decode(Ctx* c, Op& op) {
   nsplit = (d.MP + chunk - 1) / chunk;
   op.p1 = chunk;
   op.p2 = nsplit;
-  // Partials, then one arrival counter per (sequence, kv head x head group), zero between launches.
-  const size_t part_bytes = (size_t)d.B * d.H * nsplit * (d.D + 2) * sizeof(float);
-  op.scratch_bytes = part_bytes + (size_t)units * sizeof(unsigned int);
+  op.scratch_bytes = (size_t)d.B * d.H * nsplit * (d.D + 2) * sizeof(float);
   TB_CUDA(c, cudaMalloc(&op.scratch, op.scratch_bytes));
-  TB_CUDA(c, cudaMemset(op.scratch, 0, op.scratch_bytes));
   const int smem = d.D == 128 ? DecSmem<128>::TOTAL : DecSmem<64>::TOTAL;
   if (d.D == 128)
     TB_CUDA(c, cudaFuncSetAttribute(decode_tma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -512,7 +474,6 @@ int launch_decode(Ctx* c, Op& op, const uint64_t* a) {
   p.nsplit = op.p2;
   p.part_acc = (float*)op.scratch;
   p.part_ml = p.part_acc + (size_t)d.B * d.H * p.nsplit * d.D;
-  p.counters = (unsigned int*)(p.part_ml + (size_t)d.B * d.H * p.nsplit * 2);
   p.status = c->status;
   const int hgroups = (d.H / d.G + 7) / 8;
   dim3 grid(p.nsplit, d.G * hgroups, d.B);
@@ -522,6 +483,13 @@ int launch_decode(Ctx* c, Op& op, const uint64_t* a) {
     TB_CUDA(c, launch_k(c, decode_tma_kernel<64>, dim3(grid), dim3(DEC_THREADS), DecSmem<64>::TOTAL, 1, mk, mv, p));
   TB_CUDA(c, cudaGetLastError());
   c->launches += 1;
+  if (p.nsplit > 1) {
+    // (Merging in the first kernel, by the split that arrives last, was measured: 3-5 us slower
+    // per launch at the shapes that split, because every CTA pays the fence and the count.)
+    TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3((d.B * d.H + 7) / 8), dim3(256), 0, 1, p, d.D, d.P));
+    TB_CUDA(c, cudaGetLastError());
+    c->launches += 1;
+  }
   return 0;
 }
 
@@ -635,7 +603,6 @@ extern "C" int tb200_decode_attention_static(tb200_ctx* h, const int32_t* dims, 
   // this call's first kernel (the merge derives the live splits from lens, as the writers do).
   p.part_acc = g_static_scratch_addr[c->device];
   p.part_ml = p.part_acc + (size_t)d.B * d.H * nsplit * d.D;
-  p.counters = nullptr;  // merged by the second kernel: nothing in the scratch has to persist or start at zero
   p.status = c->status;
   dim3 grid(nsplit, d.G * hgroups, d.B);
   if (d.D == 128)
@@ -643,9 +610,12 @@ extern "C" int tb200_decode_attention_static(tb200_ctx* h, const int32_t* dims, 
   else
     TB_CUDA(c, launch_k(c, decode_tma_kernel<64>, dim3(grid), dim3(DEC_THREADS), DecSmem<64>::TOTAL, 1, mk, mv, p));
   TB_CUDA(c, cudaGetLastError());
-  TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3((d.B * d.H + 7) / 8), dim3(256), 0, 1, p, d.D, d.P));
-  TB_CUDA(c, cudaGetLastError());
-  c->launches += 2;
+  c->launches += 1;
+  if (nsplit > 1) {
+    TB_CUDA(c, launch_k(c, decode_combine_kernel, dim3((d.B * d.H + 7) / 8), dim3(256), 0, 1, p, d.D, d.P));
+    TB_CUDA(c, cudaGetLastError());
+    c->launches += 1;
+  }
   return 0;
 }
 
