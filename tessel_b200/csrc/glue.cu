@@ -302,12 +302,16 @@ __global__ void argmax_partial_kernel(const float* __restrict__ X, float* __rest
   const float* x = X + (size_t)row * N;
   float best = -INFINITY;
   int at = INT_MAX;
-  for (int c = threadIdx.x; c < N; c += blockDim.x) {
-    const float v = x[c];
-    if (v > best || (v == best && c < at)) {
-      best = v;
-      at = c;
+  auto take = [&](float v, int c) {
+    if (v > best || (v == best && c < at)) best = v, at = c;
+  };
+  if ((N & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    for (int c = threadIdx.x * 4; c < N; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(x + c);
+      take(v.x, c), take(v.y, c + 1), take(v.z, c + 2), take(v.w, c + 3);
     }
+  } else {
+    for (int c = threadIdx.x; c < N; c += blockDim.x) take(x[c], c);
   }
   auto merge = [](float& v, int& i, float ov, int oi) {
     if (ov > v || (ov == v && oi < i)) {
@@ -375,12 +379,20 @@ __global__ void argmax_rows_kernel(const float* __restrict__ X, int* __restrict_
   const float* x = X + (size_t)blockIdx.x * N;
   float best = x[0];
   int at = 0;
-  // Thread-strided scan keeps, per thread, the earliest index of its maximum.
-  for (int c = threadIdx.x; c < N; c += blockDim.x) {
-    const float v = x[c];
-    if (v > best || (c < at && v == best)) {
-      best = v;
-      at = c;
+  // Thread-strided scan keeps, per thread, the earliest index of its maximum. A thread's
+  // indices only grow, so a strict comparison already keeps the earliest.
+  if ((N & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    for (int c = threadIdx.x * 4; c < N; c += blockDim.x * 4) {
+      const float4 v = *reinterpret_cast<const float4*>(x + c);
+      if (v.x > best) best = v.x, at = c;
+      if (v.y > best) best = v.y, at = c + 1;
+      if (v.z > best) best = v.z, at = c + 2;
+      if (v.w > best) best = v.w, at = c + 3;
+    }
+  } else {
+    for (int c = threadIdx.x; c < N; c += blockDim.x) {
+      const float v = x[c];
+      if (v > best) best = v, at = c;
     }
   }
   auto merge = [](float& v, int& i, float ov, int oi) {

@@ -105,6 +105,11 @@ def test_residual_add_and_argmax(gpu):
     want = np.asarray([oracle.argmax(row) for row in x], i32)
     assert np.array_equal(pick, want)
     assert pick[0] == 17 and pick[1] == 4999 and pick[2] == 0 and pick[3] == 0 and pick[5] == 0
+    # A row length that is not a multiple of four takes the scalar scan.
+    y = np.ascontiguousarray(x[:, :4999])
+    y[1, 4998] = 9.0
+    (pick,) = run(gpu, "argmax_rows", [y, np.zeros(33, i32)], [1])
+    assert np.array_equal(pick, np.asarray([oracle.argmax(row) for row in y], i32))
 
 
 @pytest.mark.parametrize("R", [2, 4, 8])
