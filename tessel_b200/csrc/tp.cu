@@ -306,10 +306,11 @@ int launch_tp(Ctx* c, Op& op, const uint64_t* a) {
   const float eps = bits_f32(a[3]);
   const int which = (int)(uint32_t)a[4], do_norm = (int)(uint32_t)a[5];
   if (which < 0 || which > 1) return fail(c, op.name + ": which is 0 or 1");
-  if (c->nranks < 2) return fail(c, op.name + ": needs tb200_comm_init with at least two ranks");
+  const int nranks = (int)(uint32_t)a[6];
+  if (nranks < 2 || nranks > TP_MAX) return fail(c, op.name + ": nranks (the table's) is 2 to 8");
   // One CTA per row this rank owns; every rank launches the same grid.
   // At most one CTA per SM, so that the CTAs that wait on each other across ranks are all resident.
-  int grid = (T + c->nranks - 1) / c->nranks;
+  int grid = (T + nranks - 1) / nranks;
   if (grid > c->sm_count) grid = c->sm_count;
   if (grid > TP_SLOTS) grid = TP_SLOTS;
   if (dim <= 4 * TP_THREADS)
