@@ -7,6 +7,16 @@ the same admission rule (pages for the whole sequence reserved up front, the
 step's token budget, the batch limit), the same page order (the free list pops
 0, 1, 2, ...), slots ``page * P + offset``, packed prefill with per-row
 ``starts``, and decode steps with block tables and lengths.
+
+One extension (off by default): ``chunk``. The reference needs a prompt to fit
+one step (src/llm/sched.rs:76-81). With ``chunk > 0`` a longer prompt is
+admitted anyway and fed ``chunk`` tokens at a time as extra rows of the decode
+steps, each row attending, through the sequence's block table, to the keys
+cached so far (its own chunk's earlier tokens included: a step writes all its
+keys before its attention runs). These rows go through the paged decode
+attention, one row per token, so they cost far more per token than a prefill
+step does; the feature is for the occasional prompt that exceeds the step, not
+a replacement for prefill.
 """
 from __future__ import annotations
 
@@ -53,6 +63,7 @@ class _Seq:
     len: int  # tokens in the cache
     last: int
     left: int
+    todo: int = 0  # prompt tokens not yet in the cache (a prompt fed in chunks)
 
 
 class Scheduler:
@@ -60,8 +71,10 @@ class Scheduler:
     one call admits and prefills what fits, or decodes one token for every running sequence."""
 
     def __init__(self, e: Engine, reqs: Sequence[Request], max_batch: int, packed: bool = True,
-                 device_argmax: bool = False):
+                 device_argmax: bool = False, chunk: int = 0):
         self.e, self.reqs, self.packed, self.device_argmax = e, reqs, packed, device_argmax
+        self.chunk = max(0, min(chunk, e.lim.max_tokens - 1))
+        self.feeding: List[_Seq] = []  # sequences whose (long) prompt is still being fed in chunks
         self.start = time.perf_counter()
         # Pops yield pages 0, 1, 2, ...
         self.free: List[int] = list(range(e.lim.pages - 1, -1, -1))
@@ -76,7 +89,7 @@ class Scheduler:
         self._table_np = np.zeros((0, 0), np.int32)
 
     def done(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and not self.feeding
 
     def _choose(self, attn, toks, pos, slots, want) -> List[int]:
         if self.device_argmax:
@@ -93,9 +106,19 @@ class Scheduler:
             rid = self.waiting[0]
             r = self.reqs[rid]
             need = -(-(len(r.prompt) + r.max_new) // p)
-            if len(r.prompt) == 0 or len(r.prompt) > e.lim.max_tokens or need > e.lim.max_seq_pages:
+            long = len(r.prompt) > e.lim.max_tokens
+            if len(r.prompt) == 0 or (long and not self.chunk) or need > e.lim.max_seq_pages:
                 raise ValueError(f"request {rid}: prompt of {len(r.prompt)} tokens does not fit")
-            room = len(self.running) + len(admit) < self.max_batch and tokens + len(r.prompt) <= e.lim.max_tokens
+            busy = len(self.running) + len(self.feeding) + len(admit)
+            if long:
+                # Fed in chunks alongside the decode rows: it takes a place in the batch and its pages now.
+                if busy >= self.max_batch or need > len(self.free):
+                    break
+                self.waiting.popleft()
+                self.feeding.append(_Seq(rid, [self.free.pop() for _ in range(need)], 0, -1, r.max_new,
+                                         len(r.prompt)))
+                continue
+            room = busy < self.max_batch and tokens + len(r.prompt) <= e.lim.max_tokens
             if not room or need > len(self.free) or (not self.packed and admit):
                 break
             self.waiting.popleft()
@@ -169,6 +192,8 @@ class Scheduler:
                 else:
                     self.running.append(s)
             return "prefill"
+        if self.feeding:
+            return self._mixed_step()
         if not self.running:
             return "idle"
         t0 = time.perf_counter()
@@ -176,6 +201,58 @@ class Scheduler:
         self.absorb(self._choose(attn, toks, pos, slots, want))
         st.decode_seconds += time.perf_counter() - t0
         return "decode"
+
+    def _mixed_step(self) -> str:
+        """A decode step whose extra rows are the next chunk of each prompt that is being fed."""
+        e, p, st, reqs = self.e, self.e.lim.page, self.st, self.reqs
+        run = list(self.running)
+        toks = [s.last for s in run]
+        pos = [s.len for s in run]
+        slots = [s.pages[s.len // p] * p + s.len % p for s in run]
+        tables = [s.pages for s in run]
+        lens = [s.len + 1 for s in run]
+        want = list(range(len(run)))
+        budget = e.lim.max_tokens - len(run)
+        fed = []  # (sequence, tokens fed, row of its last prompt token or -1)
+        for s in self.feeding:
+            c = min(self.chunk, s.todo, budget)
+            if c <= 0:
+                continue
+            budget -= c
+            pr = reqs[s.id].prompt
+            for i in range(s.len, s.len + c):
+                toks.append(pr[i])
+                pos.append(i)
+                slots.append(s.pages[i // p] * p + i % p)
+                tables.append(s.pages)
+                lens.append(i + 1)
+            last = -1
+            if c == s.todo:
+                last = len(toks) - 1
+                want.append(last)
+            fed.append((s, c, last))
+        picks = self._choose(Decode(tables, lens), toks, pos, slots, want)
+        if run:
+            self.absorb(picks[:len(run)])
+        st.prompt_tokens += sum(c for _, c, _ in fed)
+        k = len(run)
+        for s, c, last in fed:
+            s.len += c
+            s.todo -= c
+            if last < 0:
+                continue
+            t = int(picks[k])
+            k += 1
+            self.feeding.remove(s)
+            self.out[s.id].tokens.append(t)
+            self.out[s.id].first_token_s = time.perf_counter() - self.start
+            s.last, s.left = t, s.left - 1
+            if s.left == 0 or t == e.cfg.eos:
+                self.out[s.id].done_s = time.perf_counter() - self.start
+                self.free.extend(s.pages)
+            else:
+                self.running.append(s)
+        return "mixed"
 
     def finish(self) -> Tuple[List[Output], Stats]:
         self.st.generated = sum(len(o.tokens) for o in self.out)
@@ -190,11 +267,12 @@ def generate(e: Engine, reqs: Sequence[Request], max_batch: int) -> Tuple[List[O
 
 
 def generate_with(e: Engine, reqs: Sequence[Request], max_batch: int, packed: bool,
-                  device_argmax: bool = False) -> Tuple[List[Output], Stats]:
+                  device_argmax: bool = False, chunk: int = 0) -> Tuple[List[Output], Stats]:
     """``generate``, choosing whether new prompts share prefill steps (``packed``) or each takes
     its own. ``device_argmax`` picks the tokens on the GPU (``Engine.step_greedy``) instead of
-    reading the logits back and choosing on the host as the reference does."""
-    s = Scheduler(e, reqs, max_batch, packed, device_argmax)
+    reading the logits back and choosing on the host as the reference does. ``chunk > 0`` admits
+    prompts longer than a step and feeds them that many tokens at a time (see the module text)."""
+    s = Scheduler(e, reqs, max_batch, packed, device_argmax, chunk)
     while not s.done():
         if s.step() == "idle" and s.waiting:
             raise ValueError(f"request {s.waiting[0]} cannot be admitted: not enough cache pages")

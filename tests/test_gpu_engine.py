@@ -116,3 +116,17 @@ def test_engine_from_a_checkpoint_directory(gpu, tmp_path):
     a, _ = generate_with(Engine(gpu, w, lim), reqs, 2, True, device_argmax=True)
     b, _ = generate_with(Engine(gpu, checkpoint.load(str(tmp_path)), lim), reqs, 2, True, device_argmax=True)
     assert [o.tokens for o in a] == [o.tokens for o in b]
+
+
+def test_long_prompt_fed_in_chunks_alongside_decodes(gpu):
+    """A prompt longer than the step, fed 48 tokens at a time as rows of the decode steps: the
+    GPU engine and the CPU engine (oracle kernels) produce the same tokens."""
+    cfg = small()
+    w = Weights.random(cfg, 23)
+    lim = Limits(page=16, pages=48, max_tokens=64, max_seq_pages=16)
+    g = np.random.default_rng(5)
+    reqs = [Request(g.integers(0, cfg.vocab, 9).tolist(), 10), Request(g.integers(0, cfg.vocab, 170).tolist(), 8)]
+    got, st = generate_with(Engine(gpu, w, lim), reqs, 2, True, device_argmax=True, chunk=48)
+    want, _ = generate_with(Engine(EmuGpu(), w, lim), reqs, 2, True, chunk=48)
+    assert st.prompt_tokens == 179
+    assert [o.tokens for o in got] == [o.tokens for o in want]

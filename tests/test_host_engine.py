@@ -39,6 +39,28 @@ def test_long_prefill_steps_pad_to_256_rows_and_change_nothing():
         assert a.tokens == b.tokens
 
 
+def test_a_prompt_longer_than_a_step_is_fed_in_chunks():
+    """Off by default (the reference refuses such a prompt, src/llm/sched.rs:76-81); with
+    ``chunk`` the long prompt rides along the decode steps and ends in the same tokens as a
+    prefill in one step on an engine large enough for it."""
+    cfg = Config.tiny()
+    w = Weights.random(cfg, 9)
+    long = [1 + (i * 31 % 250) for i in range(150)]
+    reqs = [Request([1, 9, 42, 7, 200, 13], 12), Request(long, 6), Request([3, 5, 8], 10)]
+    big = Limits(page=8, pages=96, max_tokens=256, max_seq_pages=24)
+    small = Limits(page=8, pages=96, max_tokens=64, max_seq_pages=24)
+    want, _ = generate_with(Engine(EmuGpu(), w, big), reqs, 3, True)
+    with pytest.raises(ValueError, match="does not fit"):
+        generate_with(Engine(EmuGpu(), w, small), reqs, 3, True)
+    got, st = generate_with(Engine(EmuGpu(), w, small), reqs, 3, True, chunk=40)
+    for a, b in zip(got, want):
+        assert a.tokens == b.tokens
+    assert st.prompt_tokens == sum(len(r.prompt) for r in reqs)
+    # Alone, too: nothing is running while the prompt is fed.
+    got, _ = generate_with(Engine(EmuGpu(), w, small), reqs[1:2], 1, True, chunk=33)
+    assert got[0].tokens == want[1].tokens
+
+
 def test_prefill_and_batched_decode_match_the_reference():
     cfg = Config.tiny()
     w = Weights.random(cfg, 7)
