@@ -1,4 +1,4 @@
-"""Decode throughput of the Llama-3-8B-shaped engine (BASELINE config 5) on N B200s.
+"""Decode throughput of the Llama-3-8B-shaped engine (benchmark configuration 5) on N B200s.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
@@ -423,7 +423,7 @@ def run_ours(args, wl):
     }
     if world == 1 and not args.no_micro:
         # The two other headline numbers of the path (and the prefill attention), same process:
-        # single kernels at BASELINE configs' shapes, CUDA events per launch, L2 flushed in between.
+        # single kernels at the benchmark configurations' shapes, CUDA events per launch, L2 flushed in between.
         from tessel_b200 import microbench as mb
         d = mb.decode(gpu, torch, iters=10)
         gm = mb.gemm(gpu, torch, 4096, 4096, 4096, "matmul", iters=10)

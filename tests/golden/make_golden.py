@@ -17,7 +17,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 
 
 def config1_inputs(seed: int = 1):
-    """BASELINE config 1: 4 sequences with contexts 37/128/300/511, 8 query heads, 2 KV heads,
+    """benchmark configuration 1: 4 sequences with contexts 37/128/300/511, 8 query heads, 2 KV heads,
     head_dim 64, page size 16, block tables a seeded permutation of a 128-page pool, Q/K/V
     f16 ~N(0,1), scale 1/sqrt(64)."""
     g = np.random.default_rng(seed)

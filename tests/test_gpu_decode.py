@@ -1,5 +1,5 @@
 """Paged grouped-query decode attention on the GPU against the CPU oracle and the committed
-fixture: BASELINE config 1, the reference's own test shapes (ragged lengths 37/1/64, an empty
+fixture: benchmark configuration 1, the reference's own test shapes (ragged lengths 37/1/64, an empty
 sequence, lengths that end mid-page), both head dims of the TMA path, the generic path, and at
 full Llama-3-8B decode size a linearity property that needs no oracle."""
 import os

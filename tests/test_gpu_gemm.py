@@ -70,7 +70,7 @@ def test_matmul_row_major_b(gpu, M, K, N):
 
 
 def test_matmul_4096_cubed(gpu):
-    """BASELINE config 2: A, B ~U[-1,1] seeded, f16, f32 accumulation, f16 out; 256 sampled
+    """benchmark configuration 2: A, B ~U[-1,1] seeded, f16, f32 accumulation, f16 out; 256 sampled
     entries in f64, whole rows against the oracle, and C(A, B1 + B2) = C(A, B1) + C(A, B2)
     for operands chosen so that the sums are exact."""
     n = 4096

@@ -10,7 +10,7 @@ from tessel_b200.gpu import F32
 
 pytestmark = pytest.mark.gpu
 h, f, i32 = np.float16, np.float32, np.int32
-TOL = 2e-3  # relative to the largest reference value (BASELINE north star)
+TOL = 2e-3  # relative to the largest reference value (the target for this path)
 
 
 def run(gpu, name, arrays, outs, scalars=()):

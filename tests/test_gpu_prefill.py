@@ -77,7 +77,7 @@ def test_flash_attention(gpu, H, S, D):
 
 
 def test_config3_shape_sampled(gpu):
-    """BASELINE config 3 (batch 8 x 32 heads folded into H = 256, S 4096, D 128, ~N(0,1)): a
+    """benchmark configuration 3 (batch 8 x 32 heads folded into H = 256, S 4096, D 128, ~N(0,1)): a
     few (head, row-block) programs against the oracle; and the first row of every head
     attends to itself only, so O[h, 0] == V[h, 0] exactly."""
     g = np.random.default_rng(3)

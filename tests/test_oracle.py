@@ -192,7 +192,7 @@ def test_decode_attention_gqa(r):
 
 
 def test_config1_golden():
-    """BASELINE config 1 (ctx 37/128/300/511, 8 heads, 2 kv heads, D 64, 128-page pool): the
+    """benchmark configuration 1 (ctx 37/128/300/511, 8 heads, 2 kv heads, D 64, 128-page pool): the
     committed fixture, generated by tests/golden/make_golden.py, still matches the oracle."""
     from golden.make_golden import config1_inputs
     c = config1_inputs()

@@ -40,7 +40,7 @@ def test_static_scratch_entry_point_matches_the_regular_kernel(gpu):
     r = oracle.Rng(77)
     cases = [
         (32, 8, 128, [700, 33, 1152, 16, 0, 2303]),   # Llama-3-8B heads: several KV splits
-        (8, 2, 64, [37, 128, 300, 511]),              # BASELINE config 1's shape, other data
+        (8, 2, 64, [37, 128, 300, 511]),              # benchmark configuration 1's shape, other data
     ]
     for H, G, D, lens in cases:
         q, kc, vc, table, ln, scale = paged_case(r, len(lens), H, D, 16, lens, g=G)
