@@ -16,8 +16,9 @@ prompts are prefilled through the engine first (untimed), then W warm-up decode 
 
 Both are timed with CUDA events on the stream the kernels run on, between synchronisations,
 and the maximum over ranks is taken. With N > 1 the model is tensor-parallel over the N GPUs
-(attention/KV heads and MLP columns sharded, one NCCL allreduce after o_proj and after
-down_proj), so the job is the same 256 sequences: strong scaling.
+(attention/KV heads and MLP columns sharded; the cross-rank sum after o_proj and after
+down_proj by the fused peer-memory kernel, or by one NCCL allreduce each with
+`--tp-exchange nccl`), so the job is the same 256 sequences: strong scaling.
 
 `--impl reference` times the CPU restatement of the reference's interpreter path (the
 oracle; the reference itself is Rust and cannot be built on these machines) on the host

@@ -5,8 +5,9 @@
 // [pages, P, G, D]. The reference launches one warp per (sequence, query
 // head), so each of the H/G query heads of a KV head re-reads the same pages.
 // Here one CTA serves ALL query heads of a KV head, so every page crosses HBM
-// once; long contexts are split over CTAs (split-KV) and merged by a second,
-// tiny kernel.
+// once. When that gives too few CTAs to fill the SMs, the key range is split
+// over CTAs (split-KV) and the partials are merged by a second, tiny kernel;
+// otherwise the one kernel writes the output itself.
 //
 // Fast path (P == 16, D in {64, 128}, f16): a producer warp walks the block
 // table and streams (page, kv-head) tiles into a shared-memory ring with TMA

@@ -11,16 +11,18 @@
 // (128-byte swizzle); one thread of warp 1 issues tcgen05.mma (M = 128, N = BN
 // or 2 BN, K = 16, f16 in, f32 accumulate) into tensor memory - with MT = 2 two
 // accumulators share every weight tile - and releases ring slots with
-// tcgen05.commit; warps 2-5 read the finished accumulators out of tensor memory
-// (one row per thread) and apply the epilogue. gate_up loads the Wg and Wu
+// tcgen05.commit; warps 2-9 read the finished accumulators out of tensor memory
+// (one row per thread, two warps per lane quadrant taking half the columns
+// each) and apply the epilogue. gate_up loads the Wg and Wu
 // tiles side by side so that one MMA of N = 2 BN produces both products from
 // one read of X. Rows beyond M and columns beyond N are zero-filled by TMA on
 // the way in and masked on the way out.
 //
-// The feed from L2 into an SM (about 90 GB/s) is what bounds these kernels
-// before HBM or the tensor pipe does, so tiles are as large as the shape
-// allows: a decode step's 256 rows are ONE CTA's rows, each weight tile is
-// fetched by one CTA only. Projections with few column tiles (QKV, o_proj,
+// An SM takes in about 75-100 GB/s through TMA, activation and weight tiles
+// together, so tiles are as large as the shape allows: a decode step's 256
+// rows are ONE CTA's rows, each weight tile is fetched by one CTA only.
+// Every kernel waits for its predecessor (programmatic dependent launch) only
+// after it has requested its first weight tiles, which no kernel writes. Projections with few column tiles (QKV, o_proj,
 // down_proj at decode sizes) would then leave SMs idle, so they split K over a
 // thread-block cluster: each CTA accumulates a K range, the partial tiles are
 // exchanged through distributed shared memory (every CTA owns a share of the

@@ -1,7 +1,8 @@
 // The memory-bound glue kernels of a decoder step: embedding gather, RMSNorm,
-// rotary embedding of the queries, rotary + paged KV-cache write, the final
-// norm of selected rows, and (beyond the reference) residual add and row
-// argmax. All are 16-byte vectorised; none needs shared-memory staging beyond
+// rotary embedding of the queries, rotary + paged KV-cache write (also as one
+// launch, rope_kv), the final norm of selected rows, and (beyond the
+// reference) residual add, row argmax (whole rows, or a vocabulary split
+// across ranks) and the device-side step advance. All are 16-byte vectorised; none needs shared-memory staging beyond
 // a block reduction.
 //
 // Rounding follows tessel's interpreter: every f32 product, sum and quotient

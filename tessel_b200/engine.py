@@ -8,12 +8,17 @@ same padding rules, buffer dtypes and launch order, driving
 ``libtessel_b200`` through :class:`tessel_b200.gpu.Gpu`.
 
 Beyond the reference: the step's integer inputs go up from page-locked memory
-in asynchronous copies; ``step_greedy`` picks the tokens on the device so that
-only ``len(want)`` integers come back instead of ``len(want) * vocab`` floats;
-and the model can be tensor-parallel (``rank``/``nranks``): attention and KV
-heads and the MLP columns are sharded, o_proj and down_proj produce f32
-partials that are summed across ranks (one allreduce each) before they are
-added to the residual stream.
+in asynchronous copies; ``rope_q`` and ``kv_write`` run as one launch; prefill
+steps beyond 256 rows are padded to a multiple of 256, not to a power of two;
+``step_greedy`` picks the tokens on the device so that only ``len(want)``
+integers come back instead of ``len(want) * vocab`` floats, and
+``decode_resident`` runs decode steps back to back with no host input; and the
+model can be tensor-parallel (``rank``/``nranks``): attention and KV heads and
+the MLP columns are sharded, o_proj and down_proj produce f32 partials that
+are summed across ranks before they are added to the residual stream, by one
+NCCL allreduce each or, given ``exchange``, by one kernel over peer memory that
+also does the residual add and the next RMSNorm; greedy steps then split the
+LM head's rows across the ranks too.
 """
 from __future__ import annotations
 
