@@ -28,10 +28,7 @@ namespace {
 
 constexpr int DEC_WARPS = 4;                    // consumer warps
 constexpr int DEC_THREADS = (DEC_WARPS + 1) * 32;  // + one producer warp
-#ifndef TB_DEC_STAGES
-#define TB_DEC_STAGES 8
-#endif
-constexpr int DEC_STAGES = TB_DEC_STAGES;                   // pages in flight per CTA
+constexpr int DEC_STAGES = 8;                   // pages in flight per CTA
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct DecodeParams {
