@@ -28,8 +28,16 @@ namespace {
 
 constexpr int DEC_WARPS = 4;                    // consumer warps
 constexpr int DEC_THREADS = (DEC_WARPS + 1) * 32;  // + one producer warp
-constexpr int DEC_STAGES = 8;                   // pages in flight per CTA
+#ifndef TB_DEC_STAGES
+#define TB_DEC_STAGES 8
+#endif
+constexpr int DEC_STAGES = TB_DEC_STAGES;                   // pages in flight per CTA
 constexpr float LOG2E = 1.4426950408889634f;
+// Consumer warp w takes pages w, w + DEC_WARPS, ...: with a ring depth that is a multiple of
+// DEC_WARPS a slot is always read by the same warp, which therefore waits for every one of the
+// slot's phases in turn. Any other depth would let a warp skip a phase of a slot, and a parity
+// test cannot tell a phase from the one two before it.
+static_assert(DEC_STAGES % DEC_WARPS == 0, "ring depth must be a multiple of the consumer warps");
 
 struct DecodeParams {
   const __half* Q;
