@@ -62,6 +62,21 @@ def test_against_oracle(gpu, H, G, D, P, lens):
     check(got, oracle.decode_attention(q, kc, vc, table, ln, scale), lens)
 
 
+@pytest.mark.parametrize("splits,lens", [
+    (1, [300, 0, 17, 1000, 64]),              # one split: the kernel writes O itself (and the NaN row)
+    (5, [300, 0, 17, 1000, 64, 2]),           # five splits: partials merged by the second kernel
+    (2, [1, 0, 16, 33, 2303, 512, 100]),
+])
+def test_forced_split_counts(gpu, monkeypatch, splits, lens):
+    """Both ways of finishing (direct, or split-KV partials + merge) on the same kind of input;
+    the split count is fixed when the kernel is made, so each case has its own batch size."""
+    monkeypatch.setenv("TB200_DECODE_SPLITS", str(splits))
+    r = oracle.Rng(31 + splits)
+    q, kc, vc, table, ln, scale = paged_case(r, len(lens), 32, 128, 16, lens, g=8)
+    got = decode(gpu, q, kc, vc, table, ln, scale)
+    check(got, oracle.decode_attention(q, kc, vc, table, ln, scale), lens)
+
+
 def test_paged_attention_name(gpu):
     """kernels/attention.tl:29-51 is the same computation with one KV head per query head."""
     r = oracle.Rng(22)
