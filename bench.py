@@ -443,8 +443,8 @@ def run_ours(args, wl):
             "peak_kind": pk["kind"]}
     if world == 1 and not args.no_cpu_baseline:
         import oracle
-        # About 10-20 s of CPU work: four layers and 1/8 of the LM head for half of the batch.
-        rows, nl = min(n, 128), min(cfg.layers, 4)
+        # About 10-20 s of CPU work: six layers and 1/8 of the LM head for half of the batch.
+        rows, nl = min(n, 128), min(cfg.layers, 6)
         sample_s, full_s = CpuSample(cfg, [q.len for q in s.running], rows).run(nl)
         line["cpu_baseline"] = {
             "value": n / full_s, "unit": UNIT, "cores": oracle.threads(), "kind": "port",
