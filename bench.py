@@ -20,9 +20,15 @@ and the maximum over ranks is taken. With N > 1 the model is tensor-parallel ove
 down_proj by the fused peer-memory kernel, or by one NCCL allreduce each with
 `--tp-exchange nccl`), so the job is the same 256 sequences: strong scaling.
 
+With N > 1 the line also carries `tp_check` (a small fixed-seed model run at TP N, with both
+exchanges, against the same model at TP 1 on rank 0's GPU: logits, greedy tokens, KV pages, and
+whether every rank holds the same bits of x and h) and `nccl_exchange` (the same device-resident
+step timed with the NCCL exchange when the fused one is the default, and the other way round).
+
 `--impl reference` times the CPU restatement of the reference's interpreter path (the
 oracle; the reference itself is Rust and cannot be built on these machines) on the host
-cores, on a bounded sample of the same decode step.
+cores; each of its steps is the same bounded sample of the decode step that the `cpu_baseline`
+of the default arm times once.
 """
 from __future__ import annotations
 
@@ -43,6 +49,11 @@ sys.path.insert(0, ROOT)
 
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
+# DRAM bytes moved per algorithmic byte by the decode-attention kernel, from a profiler capture
+# (dram__bytes_read + dram__bytes_write) of a smaller batch of the same shape: 295.82 MB read
+# and 5.00 MB written for 294.72 MB of algorithmic bytes; traffic grows in proportion to the
+# sequences processed, so the ratio carries to a full launch.
+DRAM_PER_ALGORITHMIC_BYTE = (295.82 + 5.00) / 294.72
 
 
 def parse():
@@ -186,6 +197,57 @@ class CpuSample:
         return t_layer * layers + t_head, (t_layer * cfg.layers + t_head * self.head_div) * (self.nseq / rows)
 
 
+def prompt_lengths(wl, seqs):
+    """The batch's prompt lengths: one seeded draw, shared by both arms."""
+    return np.random.default_rng(1).integers(wl["lo"], wl["hi"] + 1, seqs)
+
+
+def timed_contexts(plens, K, Wm):
+    """Cached tokens per sequence when the device-resident timed region starts: the prompt, the
+    warm-up steps, the three end-to-end regions of K steps, and the three steps that set the
+    resident loop up."""
+    return np.asarray(plens, np.int64) + max(Wm, 3) + E2E_REPEATS * K + 3
+
+
+def config_of(args, wl, world, seqs, plens):
+    """The `config` object of the JSON line; both arms print the same one."""
+    cfg = wl["cfg"]
+    K, Wm = args.steps, args.warmup
+    ctx_mid = float(np.mean(timed_contexts(plens, K, Wm))) + K / 2.0
+    Hl, Gl, Fl, D = cfg.heads // world, cfg.kv_heads // world, cfg.ffn // world, cfg.head_dim
+    vocab_parallel = world > 1 and cfg.vocab % world == 0 and cfg.vocab <= 1 << 24
+    head_rows = cfg.vocab // world if vocab_parallel else cfg.vocab
+    wbytes = 2.0 * (cfg.layers * ((Hl + 2 * Gl) * D * cfg.dim + cfg.dim * Hl * D + 3 * Fl * cfg.dim) + head_rows * cfg.dim)
+    kvbytes = 4.0 * Gl * D * cfg.layers * ctx_mid * seqs
+    par = f"tp{world}" + (f" ({args.tp_exchange} exchange)" if world > 1 else "")
+    return ({"workload": wl["label"], "sequences": int(seqs), "parallelism": par,
+             "l2": "inputs larger than L2 (weights + KV read per step: %.1f GB per GPU)" % ((wbytes + kvbytes) / 1e9),
+             "mean_context": ctx_mid}, wbytes, kvbytes)
+
+
+E2E_REPEATS = 3
+CPU_ROWS, CPU_LAYERS = 128, 4
+
+
+def cpu_sample_for(cfg, ctx, budget_s=None):
+    """The bounded CPU sample both arms time: CPU_LAYERS decoder layers and 1/8 of the LM head
+    for CPU_ROWS sequences. With a time budget per step, layers and then rows are halved until
+    one run fits it. Returns (sample, layers)."""
+    rows, nl = min(len(ctx), CPU_ROWS), min(cfg.layers, CPU_LAYERS)
+    smp = CpuSample(cfg, ctx, rows)
+    if budget_s is None:
+        return smp, nl
+    t, _ = smp.run(1)
+    est = lambda: t * nl  # one layer dominates; the head slice is a small part
+    while est() > budget_s and nl > 1:
+        nl //= 2
+    while est() > budget_s and rows > 8:
+        rows //= 2
+        smp = CpuSample(cfg, ctx, rows)
+        t, _ = smp.run(1)
+    return smp, nl
+
+
 def run_reference(args, wl):
     """The reference arm: rank 0 times the oracle; other ranks leave."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -193,60 +255,96 @@ def run_reference(args, wl):
     import oracle
     cfg = wl["cfg"]
     seqs = args.seqs or wl["seqs"]
-    g = np.random.default_rng(1)
-    ctx = g.integers(wl["lo"], wl["hi"] + 1, seqs)
-    rows = 16
-    # Size the sample so that K + W steps end within a few minutes.
-    smp = CpuSample(cfg, ctx, rows)
-    t, _ = smp.run()
-    while rows > 1 and t * (args.steps + args.warmup) > 150.0:
-        rows //= 2
-        smp = CpuSample(cfg, ctx, rows)
-        t, _ = smp.run()
-    for _ in range(max(0, args.warmup - 1)):
-        smp.run()
-    full = []
+    world = args.gpus
+    plens = prompt_lengths(wl, seqs)
+    config, _, _ = config_of(args, wl, world, seqs, plens)
+    ctx = timed_contexts(plens, args.steps, args.warmup).tolist()
+    # Every step is one run of the sample; K + W of them must end within a few minutes.
+    total = args.steps + args.warmup
+    smp, nl = cpu_sample_for(cfg, ctx, budget_s=170.0 / max(total, 1))
+    for _ in range(args.warmup):
+        smp.run(nl)
+    measured, full = [], []
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        full.append(smp.run()[1])
+        a, b = smp.run(nl)
+        measured.append(a)
+        full.append(b)
     wall = time.perf_counter() - t0
     sec = statistics.mean(full)
     val = seqs / sec
-    sample = (f"per step: 1 of {cfg.layers} layers and 1/8 of the LM head for {rows} of {seqs} sequences, "
-              f"scaled to the whole decode step; {wall / args.steps:.2f} s of CPU work per step")
+    sample = (f"per step: {nl} of {cfg.layers} layers and 1/8 of the LM head for {smp.rows} of {seqs} sequences at "
+              f"the contexts of the timed region, scaled to the whole decode step; {args.steps} steps measured, "
+              f"{wall / max(args.steps, 1):.2f} s of CPU work each")
     line = {"metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "impl": "reference",
-            "config": {"workload": wl["label"], "parallelism": "cpu"},
+            "warmup": args.warmup, "ms_per_step": statistics.mean(measured) * 1e3,
+            "ms_per_whole_step_extrapolated": sec * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic", "impl": "reference", "config": config,
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": oracle.threads(), "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
 # ---- our arm ---------------------------------------------------------------------------------
-def device_weights(cfg, local, seed, torch):
-    """Random-init f16 weights ~N(0, 0.02) generated on the device, this rank's shard only."""
-    from tessel_b200.model import DevArray, Layer, Weights
+def device_weights(cfg, rank, world, torch):
+    """Random-init f16 weights ~N(0, 0.02) generated on the device. Every matrix is drawn in full
+    from a seed of its own (layer, role) and this rank keeps its rows or columns of it, so the
+    model is the same model at every N: a rank's shard at TP N is a slice of the TP 1 weights."""
+    from tessel_b200.model import Config, DevArray, Layer, Weights
     gen = torch.Generator(device="cuda")
-    gen.manual_seed(seed)
     keep = []
+    H, G, D, F, dm = cfg.heads, cfg.kv_heads, cfg.head_dim, cfg.ffn, cfg.dim
+    hl, gl, fl = H // world, G // world, F // world
+    local = Config(**{**cfg.__dict__, "heads": hl, "kv_heads": gl, "ffn": fl})
 
-    def m(r, c):
+    def full(r, c, seed):
+        gen.manual_seed(seed)
         t = torch.empty((r, c), dtype=torch.float16, device="cuda")
         t.normal_(0.0, 0.02, generator=gen)
+        return t
+
+    def dev(t):
+        t = t.contiguous()
         keep.append(t)
-        return DevArray(t.data_ptr(), (r, c), np.float16, t)
+        return DevArray(t.data_ptr(), tuple(t.shape), np.float16, t)
 
     def ones(n):
-        t = torch.ones((n,), dtype=torch.float16, device="cuda")
-        keep.append(t)
-        return DevArray(t.data_ptr(), (n,), np.float16, t)
+        return dev(torch.ones((n,), dtype=torch.float16, device="cuda"))
 
-    layers = [Layer(ones(cfg.dim), m(local.qkv(), cfg.dim), m(cfg.dim, local.heads * cfg.head_dim), ones(cfg.dim),
-                    m(local.ffn, cfg.dim), m(local.ffn, cfg.dim), m(cfg.dim, local.ffn)) for _ in range(cfg.layers)]
-    # The embedding and the LM head must be the same on every rank: a generator of their own.
-    gen.manual_seed(12345)
-    return Weights(local, m(cfg.vocab, cfg.dim), layers, ones(cfg.dim), m(cfg.vocab, cfg.dim))
+    layers = []
+    for l in range(cfg.layers):
+        w = full(cfg.qkv(), dm, 16 * l + 1)
+        q = w[rank * hl * D:(rank + 1) * hl * D]
+        k = w[H * D + rank * gl * D:H * D + (rank + 1) * gl * D]
+        v = w[(H + G) * D + rank * gl * D:(H + G) * D + (rank + 1) * gl * D]
+        wqkv = dev(torch.cat([q, k, v], 0) if world > 1 else w)
+        wo = dev(full(dm, H * D, 16 * l + 2)[:, rank * hl * D:(rank + 1) * hl * D])
+        wg = dev(full(F, dm, 16 * l + 3)[rank * fl:(rank + 1) * fl])
+        wu = dev(full(F, dm, 16 * l + 4)[rank * fl:(rank + 1) * fl])
+        wd = dev(full(dm, F, 16 * l + 5)[:, rank * fl:(rank + 1) * fl])
+        layers.append(Layer(ones(dm), wqkv, wo, ones(dm), wg, wu, wd))
+    return Weights(local, dev(full(cfg.vocab, dm, 900001)), layers, ones(dm), dev(full(cfg.vocab, dm, 900002)))
+
+
+def tp_check(gpu, rank, world, dist):
+    """A small fixed-seed model at TP `world`, with the fused exchange and with NCCL, against the
+    same model at TP 1 on rank 0's GPU (tessel_b200/tpcheck.py). Returns the summaries on rank 0."""
+    from tessel_b200 import tpcheck
+
+    def gather(x):
+        out = [None] * world
+        dist.all_gather_object(out, x)
+        return out
+
+    res = {}
+    one = tpcheck.run(gpu, 0, 1) if rank == 0 else None
+    for name, exchange in (("fused", gather), ("nccl", None)):
+        mine = tpcheck.run(gpu, rank, world, exchange)
+        shards = gather({k: mine[k] for k in ("kc", "vc")} if rank else mine)
+        digests = gather(tpcheck.digest(mine))
+        if rank == 0:
+            res[name] = tpcheck.summary(one, shards, digests)
+    return res
 
 
 def run_ours(args, wl):
@@ -254,7 +352,6 @@ def run_ours(args, wl):
     import torch.distributed as dist
     from tessel_b200.engine import Engine, Limits, padded
     from tessel_b200.gpu import Gpu
-    from tessel_b200.model import Config
     from tessel_b200.sched import Request, Scheduler
 
     rank = int(os.environ.get("RANK", "0"))
@@ -283,35 +380,40 @@ def run_ours(args, wl):
     cfg = wl["cfg"]
     seqs = args.seqs or wl["seqs"]
     K, Wm = args.steps, args.warmup
-    # Decode steps this run needs from every sequence: warm-up, two timed regions, profiling.
-    need_new = max(wl["new"], Wm + 2 * K + args.profile_steps + 4)
+    # Decode steps this run needs from every sequence: warm-up, the timed regions, profiling.
+    need_new = max(wl["new"], max(Wm, 3) + (E2E_REPEATS + 2) * K + args.profile_steps + 16)
     P = 16
     max_prompt = wl["hi"]
     cfg.max_pos = max(cfg.max_pos, max_prompt + need_new)
     msp = -(-(max_prompt + need_new) // P)
     if cfg.heads % world or cfg.kv_heads % world or cfg.ffn % world:
         raise SystemExit(f"{world} ranks do not divide heads/kv_heads/ffn")
-    local = Config(**{**cfg.__dict__, "heads": cfg.heads // world, "kv_heads": cfg.kv_heads // world,
-                      "ffn": cfg.ffn // world})
-    g = np.random.default_rng(1)
-    plens = g.integers(wl["lo"], wl["hi"] + 1, seqs)
+    plens = prompt_lengths(wl, seqs)
+    g = np.random.default_rng(2)
     reqs = [Request(g.integers(0, cfg.vocab, int(n)).tolist(), need_new) for n in plens]
     pages = int(sum(-(-(int(n) + need_new) // P) for n in plens)) + 8
+    config, wbytes, kvbytes = config_of(args, wl, world, seqs, plens)
 
     gpu = Gpu(local_rank)
+    tpc = None
     if world > 1:
         ids = [gpu.comm_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         gpu.comm_init(rank, world, ids[0])
-    w = device_weights(cfg, local, 1000 + rank, torch)
+        tpc = tp_check(gpu, rank, world, dist)
+    w = device_weights(cfg, rank, world, torch)
+    local = w.cfg
     exchange = None
-    if world > 1 and args.tp_exchange == "fused":
+    if world > 1:
+        # The peer-memory exchange is always set up; `--tp-exchange nccl` merely does not use it
+        # for the headline number (the other mode is timed beside it).
         def exchange(mine):
             everyone = [None] * world
             dist.all_gather_object(everyone, mine)
             return everyone
     e = Engine(gpu, w, Limits(page=P, pages=pages, max_tokens=max_prompt, max_seq_pages=msp), rank=rank,
                nranks=world, sharded=True, exchange=exchange)
+    e.fused = world > 1 and args.tp_exchange == "fused"
     s = Scheduler(e, reqs, seqs, packed=True, device_argmax=True)
 
     # ---- prefill (untimed for the metric; reported for information) ---------------------------
@@ -329,41 +431,63 @@ def run_ours(args, wl):
     gpu.sync()
 
     clocks = Clocks(local_rank)
-    # ---- e2e: host inputs every step ------------------------------------------------------------
+    # ---- e2e: host inputs every step; E2E_REPEATS regions of K steps ----------------------------
     launches0 = gpu.kernel_launches()
-    barrier()
-    gpu.sync()
     clocks.start()
-    gpu.time_begin()
-    for _ in range(K):
-        s.step()
-    e2e_ms = gpu.time_end()
-    gpu.sync()
-    barrier()
-    e2e_ms = max_over_ranks(e2e_ms)
-    e2e_launches = gpu.kernel_launches() - launches0
+    e2e_all = []
+    for _ in range(E2E_REPEATS):
+        barrier()
+        gpu.sync()
+        gpu.time_begin()
+        for _ in range(K):
+            s.step()
+        ms = gpu.time_end()
+        gpu.sync()
+        barrier()
+        e2e_all.append(max_over_ranks(ms))
+    e2e_ms = statistics.median(e2e_all)
+    e2e_launches = (gpu.kernel_launches() - launches0) // E2E_REPEATS
 
     # ---- value: device-resident steps ---------------------------------------------------------
-    ctx0 = [q.len for q in s.running]
+    def resident(steps):
+        """`steps` device-resident decode steps between barriers; device ms, max over ranks."""
+        barrier()
+        gpu.sync()
+        gpu.time_begin()
+        picks = e.decode_resident(n, steps)
+        ms = gpu.time_end()
+        gpu.sync()
+        barrier()
+        for row in picks:
+            s.absorb(row)
+        return max_over_ranks(ms)
+
     toks, pos, slots, attn, want = s.decode_inputs()
     s.absorb(e.step_greedy(toks, pos, slots, attn, want))  # uploads the tables the resident loop walks
     for _ in range(2):
         s.absorb(e.decode_resident(n, 1)[0])
+    ctx0 = [q.len for q in s.running]
+    if ctx0 != timed_contexts(plens, K, Wm).tolist():
+        # Not expected (no sequence ends inside this run); state what was measured.
+        config["mean_context"] = float(np.mean(ctx0)) + K / 2.0
+        kvbytes = 4.0 * local.kv_heads * cfg.head_dim * cfg.layers * config["mean_context"] * n
+        config["l2"] = "inputs larger than L2 (weights + KV read per step: %.1f GB per GPU)" % ((wbytes + kvbytes) / 1e9)
     launches0 = gpu.kernel_launches()
     launches_before = launches0  # kernels launched before the device-resident timed region (a profiler's skip count)
-    barrier()
-    gpu.sync()
-    gpu.time_begin()
-    picks = e.decode_resident(n, K)
-    dev_ms = gpu.time_end()
-    gpu.sync()
-    barrier()
+    dev_ms = resident(K)
     clock_rec = clocks.stop()
-    dev_ms = max_over_ranks(dev_ms)
     dev_launches = gpu.kernel_launches() - launches0
-    ctx_mid = float(np.mean([q.len for q in s.running])) + K / 2.0
-    for row in picks:
-        s.absorb(row)
+    ctx_mid = config["mean_context"]
+
+    # ---- the other exchange, same device-resident step (N > 1) -----------------------------------
+    other = None
+    if world > 1:
+        e.fused = not e.fused
+        resident(3)  # records this mode's graph
+        other = {"exchange": "fused" if e.fused else "nccl", "ms_per_step": resident(K) / K}
+        other["value"] = n / (other["ms_per_step"] * 1e-3)
+        e.fused = not e.fused
+        resident(1)
 
     # ---- per-kernel times: the same step, every launch timed on its own (graphs off) ------------
     gpu.profile = {}
@@ -380,21 +504,14 @@ def run_ours(args, wl):
     sum_ctx = float(sum(ctx_prof)) + (args.profile_steps - 1) * n / 2.0
     att_bytes = 4.0 * Gl * D * sum_ctx + 4.0 * n * Hl * D + 4.0 * sum(-(-c // P) for c in ctx_prof) + 4.0 * n
     roof = None
-    # DRAM traffic per algorithmic byte of this kernel, from the profiler capture summarised in
-    # profiles/decode_attention_llama8b_heads_48seq.md (295.82 + 5.00 MB over 294.72 MB).
-    traffic_ratio = (295.82 + 5.00) / 294.72
     if att:
         att_ms = att[0][3] / att[0][2]
         achieved = att_bytes / (att_ms * 1e-3) / 1e9
         roof = {"kernel": "decode_attention", "bound": "hbm", "achieved": achieved, "peak": pk["hbm"], "unit": "GB/s",
-                "frac": achieved / pk["hbm"], "peak_kind": pk["kind"], "traffic": att_bytes * traffic_ratio,
+                "frac": achieved / pk["hbm"], "peak_kind": pk["kind"], "traffic": att_bytes * DRAM_PER_ALGORITHMIC_BYTE,
                 "algorithmic_bytes_per_launch": att_bytes, "ms_per_launch": att_ms,
                 "share_of_step": att[0][3] / total_prof}
     # Whole-step HBM roofline (weights once, KV once per KV head), per GPU.
-    # Greedy steps read each rank's own slice of the LM head when the vocabulary is split.
-    head_rows = cfg.vocab // world if e.vocab_parallel else cfg.vocab
-    wbytes = 2.0 * (lyr * (local.qkv() * cfg.dim + cfg.dim * Hl * D + 3 * local.ffn * cfg.dim) + head_rows * cfg.dim)
-    kvbytes = 4.0 * Gl * D * lyr * ctx_mid * n
     step_bytes = wbytes + kvbytes
     dev_step_ms = dev_ms / K
     step_roof = {"bytes_per_step_per_gpu": step_bytes, "weights_bytes": wbytes, "kv_bytes": kvbytes,
@@ -410,12 +527,10 @@ def run_ours(args, wl):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(Wm, 3),
         "ms_per_step": dev_step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic",
-        "config": {"workload": wl["label"], "sequences": n, "parallelism": f"tp{world}" + (f" ({args.tp_exchange} exchange)" if world > 1 else ""),
-                   "l2": "inputs larger than L2 (weights + KV read per step: %.1f GB per GPU)" % (step_bytes / 1e9),
-                   "mean_context": ctx_mid},
+        "dtype": "f16", "data": "synthetic", "config": config,
         "e2e": {"value": n * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * n,
-                "ms_per_step": e2e_ms / K},
+                "ms_per_step": e2e_ms / K, "ms_per_step_min": min(e2e_all) / K, "ms_per_step_max": max(e2e_all) / K,
+                "repeats": E2E_REPEATS, "value_is": "median of the repeats"},
         "gpu_launches": int(dev_launches), "e2e_gpu_launches": int(e2e_launches),
         "launches_before_timed_region": int(launches_before),
         "clocks": clock_rec,
@@ -425,6 +540,11 @@ def run_ours(args, wl):
         "prefill": {"seconds": prefill_s, "prompt_tokens": int(s.st.prompt_tokens),
                     "tok_s": s.st.prompt_tokens / prefill_s, "steps": s.st.prefill_steps},
     }
+    if tpc is not None:
+        line["tp_check"] = tpc[args.tp_exchange]
+        line["tp_check_" + ("nccl" if args.tp_exchange == "fused" else "fused")] = tpc["nccl" if args.tp_exchange == "fused" else "fused"]
+    if other is not None:
+        line[other["exchange"] + "_exchange"] = other
     if world == 1 and not args.no_micro:
         # The two other headline numbers of the path (and the prefill attention), same process:
         # single kernels at the benchmark configurations' shapes, CUDA events per launch, L2 flushed in between.
@@ -443,13 +563,13 @@ def run_ours(args, wl):
             "peak_kind": pk["kind"]}
     if world == 1 and not args.no_cpu_baseline:
         import oracle
-        # About 10-20 s of CPU work: six layers and 1/8 of the LM head for half of the batch.
-        rows, nl = min(n, 128), min(cfg.layers, 6)
-        sample_s, full_s = CpuSample(cfg, [q.len for q in s.running], rows).run(nl)
+        # One run of the sample the reference arm times per step, at the timed region's contexts.
+        smp, nl = cpu_sample_for(cfg, ctx0)
+        sample_s, full_s = smp.run(nl)
         line["cpu_baseline"] = {
             "value": n / full_s, "unit": UNIT, "cores": oracle.threads(), "kind": "port",
-            "sample": (f"{nl} of {cfg.layers} layers and 1/8 of the LM head for {rows} of {n} sequences at their "
-                       f"current contexts, scaled to the whole decode step; {sample_s:.1f} s of CPU work")}
+            "sample": (f"{nl} of {cfg.layers} layers and 1/8 of the LM head for {smp.rows} of {n} sequences at the "
+                       f"contexts of the timed region, scaled to the whole decode step; {sample_s:.1f} s of CPU work")}
     print(json.dumps(line), flush=True)
     barrier()
 

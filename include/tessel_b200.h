@@ -94,7 +94,19 @@ int tb200_kernel(tb200_ctx* ctx, const char* name, const int64_t* shapes, const 
 /* Gpu::launch (src/gpu.rs:179-217): asynchronous launch on the context's
  * stream. `args[i]` is a device pointer for an array parameter, or the bits of
  * an f32/i32 scalar in the low 32 bits (src/gpu.rs:192-193), in the kernel's
- * parameter order. */
+ * parameter order.
+ *
+ * Kernels are launched with programmatic dependent launch: a kernel may start
+ * while its predecessor on the stream drains, and waits for the predecessor
+ * itself before it touches activations. The projections (linear,
+ * linear_residual, logits, linear_f32, gate_up) request their first WEIGHT
+ * tiles before that wait. So a weight operand W must be complete before the
+ * previous kernel on the stream starts: weights written once at load time
+ * satisfy this; a W produced on the stream by the kernel launched just before
+ * (a dequantised or merged weight) does not, unless a tb200_sync or any other
+ * kernel lies in between, or the process runs with TB200_PDL=0, which restores
+ * plain stream order. matmul (both operands are activations) has no such
+ * restriction. */
 int tb200_launch(tb200_ctx* ctx, tb200_op op, const uint64_t* args, int n_args);
 
 /* Gpu::capture_begin / capture_end / replay (src/gpu.rs:233-247). */

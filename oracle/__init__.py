@@ -17,13 +17,25 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libtessel_oracle.so")
 
 
+def reference_tree() -> str:
+    """A checkout of the reference to build the f16 probe from: ``$TESSEL_REFERENCE``, else a
+    directory ``reference`` beside this repository; "" when neither holds ``src/prelude.cuh``."""
+    for cand in (os.environ.get("TESSEL_REFERENCE", ""), os.path.join(_HERE, "..", "..", "reference")):
+        if cand and os.path.isfile(os.path.join(cand, "src", "prelude.cuh")):
+            return os.path.abspath(cand)
+    return ""
+
+
 def build(force: bool = False) -> str:
-    """Compiles the oracle (and the reference f16 probe when the reference tree is present)."""
+    """Compiles the oracle (and the reference f16 probe when a reference tree is found)."""
     src = os.path.join(_HERE, "tessel_oracle.cpp")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    ref = reference_tree()
+    probe = os.path.join(_HERE, "_ref", "libprelude_probe.so")
+    stale = not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src)
+    if force or stale or (ref and not os.path.exists(probe)):
         env = dict(os.environ)
         env.pop("CXX", None)
-        subprocess.check_call(["make", "-C", _HERE, "CXX=g++"], env=env, stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-C", _HERE, "CXX=g++", "REF=" + ref], env=env, stdout=subprocess.DEVNULL)
     return _SO
 
 

@@ -113,7 +113,9 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
     return;
   }
   if (first >= npages) return;  // uniform for the CTA: nothing to do
-  const int count = min(p.chunk, npages - first);
+  // A length that runs past the block table (lens > MP * 16) is not an error in the reference:
+  // its masked table load reads 0 there, so those tokens see page 0. The last split takes them.
+  const int count = split == p.nsplit - 1 ? npages - first : min(p.chunk, npages - first);
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -141,7 +143,8 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_tma_kernel(const __grid_co
       prefetch_tmap(&mapV);
     }
     for (int j0 = 0; j0 < count; j0 += 32) {
-      const int mine = (j0 + lane < count) ? p.table[(size_t)b * p.MP + first + j0 + lane] : 0;
+      const int col = first + j0 + lane;  // beyond the table: page 0, as a masked load gives
+      const int mine = (j0 + lane < count && col < p.MP) ? p.table[(size_t)b * p.MP + col] : 0;
       const int lim = min(32, count - j0);
       for (int i = 0; i < lim; ++i) {
         const int page = __shfl_sync(0xffffffffu, mine, i);
@@ -309,7 +312,7 @@ __global__ void decode_combine_kernel(const DecodeParams p, int D, int P) {
   const int b = bh / p.H;
   const int n = p.lens[b];
   const int npages = n > 0 ? (n + P - 1) / P : 0;
-  const int ns = (npages + p.chunk - 1) / p.chunk;
+  const int ns = min((npages + p.chunk - 1) / p.chunk, p.nsplit);  // the last split takes what runs past the table
   const float* ml = p.part_ml + (size_t)bh * p.nsplit * 2;
   float mt = -INFINITY;
   for (int s = lane; s < ns; s += 32) mt = fmaxf(mt, ml[s * 2]);

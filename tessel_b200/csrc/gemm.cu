@@ -32,6 +32,8 @@
 //
 // Shapes whose row pitch is not a multiple of 16 bytes (which TMA cannot
 // address) take a plain tiled CUDA-core kernel with the same epilogues.
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace tb {
@@ -528,9 +530,39 @@ struct Plan {
   double t;
 };
 
+// Why (MT, BN, splits) cannot run `kind` on this shape, or null when it can: the tile must be
+// instantiated for the kernel, its accumulators must fit tensor memory, and a split-K cluster's
+// partial tiles must fit the ring they are received in.
+const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
+  const int epi = epi_of(kind);
+  const int nk = (g.K + BK - 1) / BK;
+  if (mt != 1 && mt != 2) return "MT is 1 or 2";
+  if (bn != 32 && bn != 64 && bn != 112 && bn != 128 && bn != 192 && bn != 256) return "BN is 32, 64, 112, 128, 192 or 256";
+  if (bn == 112 && (epi != EPI_GATE_UP || mt != 2)) return "the 112-column tile exists for gate_up with MT = 2 only";
+  if (bn == 192 && mt != 2) return "the 192-column tile exists with MT = 2 only";
+  if (kind == K_MATMUL && (bn < 64 || bn == 192)) return "matmul tiles are 64, 128 or 256 columns wide";
+  if (epi == EPI_GATE_UP && bn > 128) return "gate_up tiles are at most 128 columns wide (its MMA is 2 BN wide)";
+  const int nb = bn * (epi == EPI_GATE_UP ? 2 : 1);
+  if (mt * nb > 512) return "the accumulators exceed the 512 columns of tensor memory";
+  const int stage = mt * BM * BK * 2 + nb * BK * 2;
+  int stages = (196 * 1024) / stage;
+  if (stages > 8) stages = 8;
+  if (stages < 2) return "fewer than two ring stages fit shared memory";
+  if (s < 1 || s > 8) return "splits is 1 to 8 (the portable cluster size)";
+  if (s > 1) {
+    const int units = mt * (bn / 32);
+    if (epi == EPI_GATE_UP) return "gate_up does not split K";
+    if (s > nk) return "more splits than 64-wide K blocks";
+    if (units % s) return "splits must divide the tile's 128 x 32 units";
+    if ((s - 1) * (units / s) * UNIT_BYTES > stages * stage) return "the partial tiles of the other splits do not fit the ring";
+  }
+  return nullptr;
+}
+
 // Picks (MT, BN, splits) by a small cost model: waves of CTAs over the SMs, each CTA bound by
 // the slower of its L2-to-SM feed and its MMAs, plus its epilogue (and the partial exchange).
-Plan plan_gemm(Kind kind, const GemmShape& g, int sms) {
+// Returns the candidates, cheapest first.
+std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
   const double FEED = 90e9, TENSOR = 1636e12 / 148.0, HBM = 6.5e12;
   const int nk = (g.K + BK - 1) / BK;
   const int epi = epi_of(kind);
@@ -539,25 +571,15 @@ Plan plan_gemm(Kind kind, const GemmShape& g, int sms) {
   // The 112-column gate_up tile is instantiated but measured slower than 128 at the decode
   // shapes (128 CTAs of 224 MMA columns against 112 CTAs of 256), so only a forced plan picks it.
   const int bns[] = {256, 192, 128, 64, 32};
-  Plan best = {1, 64, 1, 1e30};
+  std::vector<Plan> all;
   for (int mt = 1; mt <= 2; ++mt) {
     if (mt == 2 && g.M <= BM) continue;
     for (int bn : bns) {
-      if (kind == K_MATMUL && (bn < 64 || bn == 192)) continue;
-      if (epi == EPI_GATE_UP && bn > 128) continue;
-      if (bn == 192 && mt == 1) continue;
-      const int nb = bn * nbf;
-      if (mt * nb > 512) continue;
-      const int stage = mt * BM * BK * 2 + nb * BK * 2;
-      int stages = (196 * 1024) / stage;
-      if (stages > 8) stages = 8;
-      if (stages < 2) continue;
       for (int s = 1; s <= 4; s *= 2) {
-        const int units = mt * (bn / 32);
-        if (s > 1) {
-          if (epi == EPI_GATE_UP || nk < 8 * s || units % s) continue;
-          if ((s - 1) * (units / s) * UNIT_BYTES > stages * stage) continue;
-        }
+        if (plan_error(kind, g, mt, bn, s)) continue;
+        if (s > 1 && nk < 8 * s) continue;
+        const int nb = bn * nbf;
+        const int stage = mt * BM * BK * 2 + nb * BK * 2;
         const long long mtiles = (g.M + mt * BM - 1) / (mt * BM), ntiles = (g.N + bn - 1) / bn;
         const long long ctas = mtiles * ntiles * s;
         const long long waves = (ctas + sms - 1) / sms;
@@ -569,11 +591,13 @@ Plan plan_gemm(Kind kind, const GemmShape& g, int sms) {
         double t = waves * ((t_feed > t_mma ? t_feed : t_mma) + 1.5e-6 + t_epi);
         const double floor_t = (2.0 * g.M * g.K + 2.0 * nbf * (double)g.N * g.K + (double)out_bytes * g.M * g.N) / HBM;
         if (t < floor_t) t = floor_t;
-        if (t < best.t) best = {mt, bn, s, t};
+        all.push_back({mt, bn, s, t});
       }
     }
   }
-  return best;
+  std::stable_sort(all.begin(), all.end(), [](const Plan& a, const Plan& b) { return a.t < b.t; });
+  if (all.empty()) all.push_back({1, 64, 1, 1e30});
+  return all;
 }
 
 }  // namespace
@@ -600,16 +624,18 @@ int make_gemm(Ctx* c, Op& op) {
   const bool tma_ok = g.K > 0 && g.K % 8 == 0 && (op.kind != K_MATMUL || g.N % 8 == 0);
   op.p0 = tma_ok ? 1 : 0;
   if (!tma_ok) return 0;
-  Plan pl = plan_gemm(op.kind, g, c->sm_count);
-  // TB200_GEMM_PLAN="mt,bn,splits" overrides the choice (tuning and tests).
+  Plan pl = plan_gemm(op.kind, g, c->sm_count)[0];
+  // TB200_GEMM_PLAN="mt,bn,splits" overrides the choice (tuning and tests). A value that does
+  // not parse, or a tile this kernel and shape cannot run, is an error: a mistyped plan must not
+  // pass a test on the default tile.
   if (const char* e = getenv("TB200_GEMM_PLAN")) {
     int a = 0, b = 0, d = 0;
-    if (sscanf(e, "%d,%d,%d", &a, &b, &d) == 3) {
-      const int nk = (g.K + BK - 1) / BK;
-      const bool ok = (a == 1 || a == 2) && d >= 1 && d <= 8 && d <= nk && (d == 1 || op.kind != K_GATE_UP) &&
-                      (d == 1 || (a * (b / 32)) % d == 0);
-      if (ok) pl = {a, b, d, 0.0};
-    }
+    char tail = 0;
+    if (sscanf(e, "%d,%d,%d%c", &a, &b, &d, &tail) != 3)
+      return bad((std::string("TB200_GEMM_PLAN=\"") + e + "\" is not MT,BN,splits").c_str());
+    if (const char* why = plan_error(op.kind, g, a, b, d))
+      return bad((std::string("TB200_GEMM_PLAN=\"") + e + "\": " + why).c_str());
+    pl = {a, b, d, 0.0};
   }
   op.p1 = pl.mt;
   op.p2 = pl.bn;

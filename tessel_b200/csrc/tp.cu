@@ -16,21 +16,30 @@
 //      all-gather, pulled: a pushed copy would need a system-wide fence that waits for every
 //      remote store to be acknowledged, measured at 6-9 us per call). The owner publishes a row
 //      in a staging buffer whose every 8 bytes hold two halves and the call's epoch, written
-//      and read as units, so a reader knows from the data itself whether it is current and
-//      polls the row directly: no "rows are ready" flag, no release fence.
+//      and read as ONE 64-bit value each (a single-copy-atomic access: payload and tag cannot be
+//      seen torn), so a reader knows from the data itself whether it is current and polls the
+//      row directly: no "rows are ready" flag, no release fence.
 //
 // Between layers only h is gathered: the residual stream stays distributed (a rank's x is
 // current in the rows it owns), because nothing but this kernel reads it. The last call of a
 // step (do_norm = 0) gathers x instead, for the final norm and the LM head, behind a second
-// flag exchange ("my rows are ready", a release).
+// flag exchange ("my rows are ready", a release), and closes with a third ("I have finished
+// reading"): the peers copy the rows straight out of this rank's x, and the very next kernel of
+// a step (embed) overwrites x, so the call may not return before every peer is done with it.
 //
 // Sums are taken in rank order by one owner, so x and h are bit-identical on all ranks, which
 // keeps the ranks' greedy tokens in lockstep. Flag waits are bounded: on time-out the kernel
 // raises the context's status word and returns.
 //
-// Why the buffers can be reused without a closing barrier: a rank overwrites its partial, or
-// its own x / h rows, only after step 1 of a later call, i.e. after every peer has begun that
-// call and therefore finished reading in this one.
+// Why the partial and staging buffers can be reused without a closing barrier: a rank
+// overwrites its partial, or its staged rows, only after step 1 of a later call, i.e. after
+// every peer has begun that call and therefore finished reading in this one. (x is the
+// exception, hence the third exchange above.)
+//
+// Step 1's signal is a relaxed store: what it announces was written by the PREVIOUS kernel of
+// the stream, and a kernel's global writes are complete and visible system-wide when its
+// successor starts (the stream order; with programmatic dependent launch, after
+// griddepcontrol.wait). No fence of this kernel could add anything to that.
 #include "common.cuh"
 
 namespace tb {
@@ -40,14 +49,15 @@ namespace {
 constexpr int TP_MAX = 8;
 constexpr int TP_SLOTS = 4096;  // CTAs a launch may have (rows of the largest step / ranks)
 constexpr int TP_THREADS = 1024;
+constexpr int TP_PHASES = 4;  // flag words per (slot, sender): partial ready, x rows ready, done reading, spare
 
 // Lives in device memory; written once by the host after the ranks exchanged IPC handles.
 struct TpTable {
   float* part[2][TP_MAX];   // the two partial-product buffers of every rank
   float* x[TP_MAX];         // residual stream of every rank
   __half* h[TP_MAX];        // normalised activations of every rank
-  uint4* stage[TP_MAX];     // [T, dim/4]: a rank's own h rows as {2 halves, epoch, 2 halves, epoch}
-  unsigned int* flags[TP_MAX];  // [TP_SLOTS][2 phases][TP_MAX senders]
+  uint4* stage[TP_MAX];     // [T, dim/4]: a rank's own h rows as two 64-bit units {2 halves | epoch << 32}
+  unsigned int* flags[TP_MAX];  // [TP_SLOTS][TP_PHASES][TP_MAX senders]
   unsigned int* epoch;      // [TP_SLOTS], local: launches this slot has taken part in
   int rank, nranks;
 };
@@ -73,13 +83,20 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* p) {
                : "memory");
   return v;
 }
-__device__ __forceinline__ uint4 ld_sys_u4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
+// Two 64-bit units {payload | tag << 32}: each unit is one scalar access, so its payload and its
+// tag are always from the same store.
+struct Unit2 {
+  unsigned long long a, b;
+};
+__device__ __forceinline__ Unit2 ld_sys_units(const uint4* p) {
+  Unit2 v;
+  asm volatile("ld.relaxed.sys.global.v2.b64 {%0,%1}, [%2];" : "=l"(v.a), "=l"(v.b) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void st_sys_units(uint4* p, unsigned int lo0, unsigned int lo1, unsigned int tag) {
+  const unsigned long long a = (unsigned long long)lo0 | ((unsigned long long)tag << 32);
+  const unsigned long long b = (unsigned long long)lo1 | ((unsigned long long)tag << 32);
+  asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1,%2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
 
 // Thread `tid` < nranks signals peer `tid` and waits for peer `tid`'s signal of this epoch.
@@ -89,12 +106,12 @@ __device__ __forceinline__ void exchange_flags(const TpTable& tb_, int slot, int
                                                bool release, unsigned int* status, unsigned int code) {
   const int tid = threadIdx.x;
   if (tid < tb_.nranks && tid != tb_.rank) {
-    unsigned int* theirs = tb_.flags[tid] + ((size_t)slot * 2 + phase) * TP_MAX + tb_.rank;
+    unsigned int* theirs = tb_.flags[tid] + ((size_t)slot * TP_PHASES + phase) * TP_MAX + tb_.rank;
     if (release)
       st_release_sys(theirs, epoch);
     else
       st_relaxed_sys(theirs, epoch);
-    const unsigned int* mine = tb_.flags[tb_.rank] + ((size_t)slot * 2 + phase) * TP_MAX + tid;
+    const unsigned int* mine = tb_.flags[tb_.rank] + ((size_t)slot * TP_PHASES + phase) * TP_MAX + tid;
     const unsigned long long t0 = globaltimer();
     unsigned int spins = 0;
     // Epochs only grow; a peer that is a launch ahead has already passed this one.
@@ -115,7 +132,7 @@ __device__ __forceinline__ void exchange_flags(const TpTable& tb_, int slot, int
 #define TP_TRACE(k)                                                                                      \
   do {                                                                                                   \
     if (blockIdx.x == 0 && threadIdx.x == 0)                                                             \
-      reinterpret_cast<unsigned long long*>(tb_.flags[tb_.rank] + (size_t)(TP_SLOTS - 64) * 2 * TP_MAX)[k] = globaltimer(); \
+      reinterpret_cast<unsigned long long*>(tb_.flags[tb_.rank] + (size_t)(TP_SLOTS - 64) * TP_PHASES * TP_MAX)[k] = globaltimer(); \
   } while (0)
 #else
 #define TP_TRACE(k) \
@@ -207,8 +224,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
           y.y = pack_h2(__fmul_rn(__fmul_rn(acc[i].z, rs), __low2float(w23)),
                         __fmul_rn(__fmul_rn(acc[i].w, rs), __high2float(w23)));
           *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)row * dim + c) = y;
-          // Each 8-byte half of this store is one unit for a reader (payload and its epoch).
-          tb_.stage[rank][((size_t)row * dim + c) >> 2] = make_uint4(y.x, epoch, y.y, epoch);
+          st_sys_units(tb_.stage[rank] + (((size_t)row * dim + c) >> 2), y.x, y.y, epoch);
         }
       }
     }
@@ -221,13 +237,16 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
       for (int i = 0; i < PER; ++i) {
         const int c = (threadIdx.x + i * TP_THREADS) * 4;
         if (c < dim) {
-          uint4 v[TP_MAX];
+          Unit2 v[TP_MAX];
           unsigned int pending = 0;
+          auto current = [&](const Unit2& u) {
+            return (unsigned int)(u.a >> 32) == epoch && (unsigned int)(u.b >> 32) == epoch;
+          };
 #pragma unroll
           for (int r = 0; r < TP_MAX; ++r)
             if (r < n && r != rank && base + r < T) {
-              v[r] = ld_sys_u4(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
-              if (v[r].y != epoch || v[r].w != epoch) pending |= 1u << r;
+              v[r] = ld_sys_units(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
+              if (!current(v[r])) pending |= 1u << r;
             }
           if (pending) {
             const unsigned long long t0 = globaltimer();
@@ -236,8 +255,8 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
 #pragma unroll
               for (int r = 0; r < TP_MAX; ++r)
                 if (pending & (1u << r)) {
-                  v[r] = ld_sys_u4(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
-                  if (v[r].y == epoch && v[r].w == epoch) pending &= ~(1u << r);
+                  v[r] = ld_sys_units(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
+                  if (current(v[r])) pending &= ~(1u << r);
                 }
               if ((++spins & 63u) == 0) {
                 if (*(volatile unsigned int*)status != 0) break;
@@ -251,7 +270,8 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
 #pragma unroll
           for (int r = 0; r < TP_MAX; ++r)
             if (r < n && r != rank && base + r < T)
-              *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)(base + r) * dim + c) = make_uint2(v[r].x, v[r].z);
+              *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)(base + r) * dim + c) =
+                  make_uint2((unsigned int)v[r].a, (unsigned int)v[r].b);
         }
       }
     }
@@ -279,6 +299,12 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
         }
       }
     }
+    // 3c. The peers read this rank's rows out of x itself, which the next step's first kernel
+    // overwrites: stay until each of them says it has finished (its loads have returned: the
+    // values were stored before its barrier).
+    __syncthreads();
+    exchange_flags(tb_, blockIdx.x, 2, epoch, false, status, 404);
+    __syncthreads();
   }
   TP_TRACE(4);
   if (threadIdx.x == 0) tb_.epoch[blockIdx.x] = epoch;
@@ -325,7 +351,7 @@ int launch_tp(Ctx* c, Op& op, const uint64_t* a) {
 }
 
 size_t tp_table_bytes() { return sizeof(TpTable); }
-size_t tp_flag_bytes() { return (size_t)TP_SLOTS * 2 * TP_MAX * sizeof(unsigned int); }
+size_t tp_flag_bytes() { return (size_t)TP_SLOTS * TP_PHASES * TP_MAX * sizeof(unsigned int); }
 size_t tp_epoch_bytes() { return (size_t)TP_SLOTS * sizeof(unsigned int); }
 
 // Fills a host copy of the table. Pointer arrays are indexed by rank.

@@ -190,6 +190,10 @@ class Engine:
             self.head_slice = Buf(self.head.ptr + rank * vs * cfg.dim * 2, vs * cfg.dim * 2)
             self.pairs = a(nranks * t * 2 * 4)
         self.tp_table: Optional[Buf] = None
+        # With the peer-memory exchange set up, ``fused = False`` falls back to the NCCL path
+        # (linear_f32 -> allreduce -> residual_add -> rmsnorm) from the next step on; every rank
+        # must switch at the same step.
+        self.fused = nranks > 1 and exchange is not None
         if nranks > 1 and exchange is not None:
             _, fb, eb = gpu.tp_sizes()
             self.part2 = a(t * cfg.dim * 4)
@@ -269,7 +273,7 @@ class Engine:
         if (not prefill) and self.graphs and g.profile is None and bw == t:
             # A decode step of this size: replay its recorded launches, or run
             # them and record them for the next time.
-            key = (t, greedy)
+            key = (t, greedy, self.fused)
             if key in self._graph:
                 g.replay(self._graph[key])
             else:
@@ -380,7 +384,7 @@ class Engine:
             g.launch(radd, [self.x, self.part])
 
         g.launch(embed, [self.tok, self.embed, self.x])
-        if self.tp_table is not None:
+        if self.tp_table is not None and self.fused:
             self._launch_layers_fused(t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale)
             self._launch_head(t, bw, greedy, eps)
             return

@@ -95,6 +95,21 @@ def test_out_of_range_pages_read_zero(gpu):
     check(got, oracle.decode_attention(q, kc, vc, table, ln, scale), [48, 80])
 
 
+@pytest.mark.parametrize("splits", [1, 3])
+def test_lengths_past_the_block_table_see_page_zero(gpu, monkeypatch, splits):
+    """A length beyond MP * P (the device-side step advance can grow one there): the reference's
+    masked table load reads 0 past the row, so those tokens attend to page 0; nothing reads past
+    the table or the split scratch, with one split and with several."""
+    monkeypatch.setenv("TB200_DECODE_SPLITS", str(splits))
+    r = oracle.Rng(40 + splits)
+    lens = [70, 200, 16 * 9 + 5, 40 + splits]  # the table below is 8 pages wide: 128 tokens
+    q, kc, vc, table, ln, scale = paged_case(r, len(lens), 32, 128, 16, [min(l, 128) for l in lens], g=8)
+    table = np.ascontiguousarray(table[:, :8])
+    ln = np.asarray(lens, i32)
+    got = decode(gpu, q, kc, vc, table, ln, scale)
+    check(got, oracle.decode_attention(q, kc, vc, table, ln, scale), lens)
+
+
 def test_llama8b_decode_size_properties(gpu):
     """Llama-3-8B decode shape (256 sequences, 32 heads on 8 KV heads, D 128, contexts up to
     2304) on a 2 GB cache: (1) a sampled subset of sequences matches the oracle; (2) with V set

@@ -43,6 +43,30 @@ def test_a_peer_that_never_arrives_is_reported_and_the_context_survives(gpu):
         gpu.launch(k, [table, w, x, F32(1e-5), I32(0), I32(1), I32(1)])
 
 
+def test_the_x_gather_stays_until_the_peers_have_finished_reading(gpu):
+    """The last call of a step (do_norm = 0) lets the peers copy rows straight out of this rank's
+    x, and the next step's first kernel overwrites x: the call must not return before every peer
+    has said it is done. Here the peer's "partial ready" and "rows ready" flags are preset and
+    its "finished reading" flag never comes: the kernel must give up in exactly that wait
+    (status 404), which shows the wait is there; the context stays usable."""
+    n, T, dim = 2, 16, 256
+    _, fb, eb = gpu.tp_sizes()
+    z = lambda nbytes: gpu.alloc(nbytes)
+    parts = [[z(T * dim * 4) for _ in range(n)] for _ in range(2)]
+    xs, hs, stages = [z(T * dim * 4) for _ in range(n)], [z(T * dim * 2) for _ in range(n)], [z(T * dim * 4) for _ in range(n)]
+    fl = np.full(fb // 4, 1000, np.uint32).reshape(-1, 4, 8)   # [slot][phase][sender]
+    fl[:, 2, :] = 0                                             # nobody ever finishes reading
+    flags = [gpu.tensor(fl), z(fb)]
+    raw = gpu.tp_table(0, n, parts[0], parts[1], xs, hs, stages, flags, z(eb))
+    table = gpu.tensor(np.frombuffer(raw, np.uint8).copy())
+    w = gpu.tensor(np.ones(dim, np.float16))
+    k = gpu.kernel("tp_reduce_norm", [[table.bytes], [dim], [T, dim]])
+    gpu.launch(k, [table, w, xs[0], F32(1e-5), I32(1), I32(0), I32(n)])
+    with pytest.raises(GpuError, match="status 404"):
+        gpu.sync()
+    gpu.sync()
+
+
 @pytest.mark.parametrize("n,T,dim", [(2, 16, 256), (3, 20, 8192), (8, 256, 4096), (4, 37, 1024)])
 def test_one_rank_of_a_group_whose_peers_are_buffers(gpu, n, T, dim):
     """The arithmetic and the data movement of ``tp_reduce_norm`` for rank 0 of ``n``, on one GPU
