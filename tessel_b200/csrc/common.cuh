@@ -119,10 +119,11 @@ int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint6
                   const uint64_t* x, const uint64_t* h, const uint64_t* stage, const uint64_t* flags, uint64_t epoch);
 int launch_prefill(Ctx* c, Op& op, const uint64_t* a);
 
-// Launches `kern` on the context's stream, as a cluster of (1, 1, cluster_z) when cluster_z > 1.
+// Launches `kern` on the context's stream, as a cluster of (cluster_x, 1, cluster_z) when that
+// is more than one CTA.
 template <class... KArgs, class... Args>
-inline cudaError_t launch_k(Ctx* c, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_z,
-                            Args&&... args) {
+inline cudaError_t launch_kc(Ctx* c, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x,
+                             int cluster_z, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -130,9 +131,9 @@ inline cudaError_t launch_k(Ctx* c, void (*kern)(KArgs...), dim3 grid, dim3 bloc
   cfg.stream = c->stream;
   cudaLaunchAttribute at[2];
   int n = 0;
-  if (cluster_z > 1) {
+  if (cluster_x * cluster_z > 1) {
     at[n].id = cudaLaunchAttributeClusterDimension;
-    at[n].val.clusterDim.x = 1;
+    at[n].val.clusterDim.x = (unsigned)cluster_x;
     at[n].val.clusterDim.y = 1;
     at[n].val.clusterDim.z = (unsigned)cluster_z;
     ++n;
@@ -145,6 +146,13 @@ inline cudaError_t launch_k(Ctx* c, void (*kern)(KArgs...), dim3 grid, dim3 bloc
   cfg.attrs = at;
   cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+// The common case: a cluster of (1, 1, cluster_z).
+template <class... KArgs, class... Args>
+inline cudaError_t launch_k(Ctx* c, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_z,
+                            Args&&... args) {
+  return launch_kc(c, kern, grid, block, smem, 1, cluster_z, static_cast<Args&&>(args)...);
 }
 
 inline float bits_f32(uint64_t v) {
@@ -294,6 +302,50 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
+}
+
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster whose ranks differ in bit 0 run one MMA of
+// M = 256 together. Each holds 128 rows of A and half of B's rows in its own shared memory, at
+// the same offsets; the even CTA issues the MMA; each gets its 128 rows of D in its own tensor
+// memory. Tensor memory is allocated by the same warp of both CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* slot_in_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_in_smem)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at `bar`'s offset in every CTA of `cta_mask` (cluster ranks) once every
+// MMA issued so far by this thread is done: the pair's ring slots are freed in both CTAs at once.
+// (A barrier signal, not a data copy: no load of any kind is broadcast here.)
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(cta_mask)
+               : "memory");
+}
+// A TMA tile load into THIS CTA's shared memory whose completion is counted on a barrier of the
+// pair's even CTA (`bar_cluster_addr`: a shared::cluster address from cluster_map).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int x,
+                                                 int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(smem_u32(dst)),
+      "l"((uint64_t)m), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
 }
 
 // 32 lanes x 32 columns of f32 from TMEM: thread i of the warp gets lane

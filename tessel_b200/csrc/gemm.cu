@@ -45,6 +45,7 @@ enum Epi : int { EPI_F16 = 0, EPI_RESID = 1, EPI_F32 = 2, EPI_GATE_UP = 3 };
 constexpr int BM = 128, BK = 64;
 constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
 constexpr int UNIT_BYTES = 128 * 32 * 4;  // one 128-row x 32-column f32 unit of a partial tile
+constexpr int PAIR = 3;                   // plan code of the CTA-pair kernel (where MT is 1 or 2 otherwise)
 
 #ifdef TB200_TRACE
 __device__ unsigned long long* g_trace = nullptr;  // [CTA][16] timestamps (ns), development builds only
@@ -76,7 +77,6 @@ struct GemmCfg {
   static constexpr int TMEM_COLS = COLS <= 32 ? 32 : COLS <= 64 ? 64 : COLS <= 128 ? 128 : COLS <= 256 ? 256 : 512;
   static constexpr int BAR_OFF = STAGES * STAGE;
   static constexpr int SMEM = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;
-  static constexpr int UNITS = MT * (BN / 32);
   static_assert(NB % 16 == 0 && NB <= 256 && COLS <= 512, "UMMA N / TMEM columns");
   static_assert(BN % 32 == 0 || EPI == EPI_GATE_UP, "only gate_up has a ragged last chunk");
   static_assert(STAGES >= 2, "ring too shallow");
@@ -134,6 +134,124 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
 #pragma unroll
       for (int j = 0; j < 32; ++j)
         if (j < ncols && col0 + j < p.N) y[j] = EPI == EPI_RESID ? __fadd_rn(y[j], v[j]) : v[j];
+    }
+  }
+}
+
+// The epilogue of one CTA: warps 2-9 read the CTA's MT x 128 rows of the finished accumulators
+// out of tensor memory (TMEM lane quadrant = warp % 4, one output row per thread; the two warps
+// of a quadrant take alternate 32-column chunks) and store them. With S > 1 the S CTAs that
+// split K first exchange partial tiles through distributed shared memory: the tile's 128 x 32
+// units are dealt round-robin to the splits, every CTA stores its partial of a unit into the
+// ring (idle by then) of the unit's owner, and the owner adds the partials in split order.
+// `split` is this CTA's index among the S; the CTA holding split s of the same tile has cluster
+// rank s * rank_stride + rank_off.
+template <int MT, int BN, int NB, int EPI>
+__device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem, unsigned char* smem,
+                                              uint64_t* acc_full, int m0, int n0, int S, uint32_t split,
+                                              uint32_t rank_stride, uint32_t rank_off) {
+  constexpr int UNITS = MT * (BN / 32);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool epi = warp >= 2;
+  const int q = warp & 3;
+  const int eh = (warp - 2) >> 2;
+  const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+  const bool tracer = warp == 2 && lane == 0;
+  if (epi) {
+    pdl_wait();  // the epilogue reads and writes buffers other kernels touch
+    mbar_wait(acc_full, 0, p.status, 203);
+    tc_fence_after();
+    if (tracer) TB_TRACE(4);
+  }
+  if (S == 1) {
+    if (epi) {
+#pragma unroll 1
+      for (int mt = 0; mt < MT; ++mt) {
+        const int row = m0 + mt * BM + q * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (((c0 >> 5) & 1) != eh) continue;
+          uint32_t r[32];
+          float v[32];
+          tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+          if (EPI == EPI_GATE_UP) {
+            uint32_t r2[32];
+            tmem_ld32(tmem + lane_base + mt * NB + BN + c0, r2);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j]));
+          } else {
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          }
+          store_chunk<EPI>(p, row, n0 + c0, v, BN - c0 < 32 ? BN - c0 : 32);
+        }
+      }
+    }
+  } else {
+    // Split K: exchange partial tiles through distributed shared memory.
+    constexpr int CH = BN / 32;
+    const int per = UNITS / S;  // units each CTA owns (the host picks S dividing UNITS)
+    const uint32_t crank = split;
+    __syncwarp();
+    cluster_sync();  // every CTA of the cluster has finished its MMAs: all rings are free
+    if (tracer) TB_TRACE(5);
+    float* recv = (float*)smem;  // [(S - 1) senders][per][8 float4 columns][128 rows]
+    const int rit = q * 32 + lane;  // row within the 128-row unit
+    if (epi) {
+      for (int u = 0; u < UNITS; ++u) {
+        const uint32_t owner = (uint32_t)(u % S);
+        if (owner == crank || ((u / S) & 1) != eh) continue;
+        const int mt = u / CH, c0 = (u % CH) * 32;
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+        tmem_ld_wait();
+        const uint32_t sidx = crank < owner ? crank : crank - 1;  // my place among the owner's senders
+        const uint32_t local = smem_u32(recv) + (sidx * per + u / S) * UNIT_BYTES + rit * 16;
+        const uint32_t remote = cluster_map(local, owner * rank_stride + rank_off);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          st_cluster_f4(remote + j * 2048, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+      }
+    }
+    if (tracer) TB_TRACE(6);
+    __syncwarp();
+    cluster_sync();  // all partials have landed
+    if (tracer) TB_TRACE(7);
+    if (epi) {
+      for (int slot = eh; slot < per; slot += 2) {
+        const int u = slot * S + (int)crank;
+        const int mt = u / CH, c0 = (u % CH) * 32;
+        uint32_t r[32];
+        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+        tmem_ld_wait();
+        float v[32];
+        // Partials are added in rank order 0, 1, ..., S-1 whatever the timing.
+        for (int s = 0; s < S; ++s) {
+          if ((uint32_t)s == crank) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = s == 0 ? __uint_as_float(r[j]) : __fadd_rn(v[j], __uint_as_float(r[j]));
+          } else {
+            const int sidx = (uint32_t)s < crank ? s : s - 1;
+            const float4* src = (const float4*)((const unsigned char*)recv + (sidx * per + slot) * UNIT_BYTES) + rit;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 t = src[j * 128];
+              if (s == 0) {
+                v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
+              } else {
+                v[4 * j] = __fadd_rn(v[4 * j], t.x);
+                v[4 * j + 1] = __fadd_rn(v[4 * j + 1], t.y);
+                v[4 * j + 2] = __fadd_rn(v[4 * j + 2], t.z);
+                v[4 * j + 3] = __fadd_rn(v[4 * j + 3], t.w);
+              }
+            }
+          }
+        }
+        store_chunk<EPI>(p, m0 + mt * BM + rit, n0 + c0, v);
+      }
     }
   }
 }
@@ -240,116 +358,151 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   }
 
-  // ---- epilogue: warps 2-9, TMEM lane quadrant = warp % 4, one output row per thread; the two
-  // warps of a quadrant take alternate column chunks (or exchange units) ----
-  const bool epi = warp >= 2;
-  const int q = warp & 3;
-  const int eh = (warp - 2) >> 2;
-  const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+  tile_epilogue<MT, BN, NB, EPI>(p, tmem, smem, acc_full, m0, n0, S, S > 1 ? cluster_ctarank() : 0u, 1u, 0u);
   const bool tracer = warp == 2 && lane == 0;
-  if (epi) {
-    pdl_wait();  // the epilogue reads and writes buffers other kernels touch
-    mbar_wait(acc_full, 0, p.status, 203);
-    tc_fence_after();
-    if (tracer) TB_TRACE(4);
-  }
-  if (S == 1) {
-    if (epi) {
-#pragma unroll 1
-      for (int mt = 0; mt < MT; ++mt) {
-        const int row = m0 + mt * BM + q * 32 + lane;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (((c0 >> 5) & 1) != eh) continue;
-          uint32_t r[32];
-          float v[32];
-          tmem_ld32(tmem + lane_base + mt * NB + c0, r);
-          if (EPI == EPI_GATE_UP) {
-            uint32_t r2[32];
-            tmem_ld32(tmem + lane_base + mt * NB + BN + c0, r2);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j]));
-          } else {
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          }
-          store_chunk<EPI>(p, row, n0 + c0, v, BN - c0 < 32 ? BN - c0 : 32);
-        }
-      }
-    }
-  } else {
-    // Split K: exchange partial tiles through distributed shared memory.
-    constexpr int CH = BN / 32;
-    const int per = Cfg::UNITS / S;  // units each CTA owns (the host picks S dividing UNITS)
-    const uint32_t crank = cluster_ctarank();
-    __syncwarp();
-    cluster_sync();  // every CTA of the cluster has finished its MMAs: all rings are free
-    if (tracer) TB_TRACE(5);
-    float* recv = (float*)smem;  // [(S - 1) senders][per][8 float4 columns][128 rows]
-    const int rit = q * 32 + lane;  // row within the 128-row unit
-    if (epi) {
-      for (int u = 0; u < Cfg::UNITS; ++u) {
-        const uint32_t owner = (uint32_t)(u % S);
-        if (owner == crank || ((u / S) & 1) != eh) continue;
-        const int mt = u / CH, c0 = (u % CH) * 32;
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
-        tmem_ld_wait();
-        const uint32_t sidx = crank < owner ? crank : crank - 1;  // my place among the owner's senders
-        const uint32_t local = smem_u32(recv) + (sidx * per + u / S) * UNIT_BYTES + rit * 16;
-        const uint32_t remote = cluster_map(local, owner);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          st_cluster_f4(remote + j * 2048, __uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-      }
-    }
-    if (tracer) TB_TRACE(6);
-    __syncwarp();
-    cluster_sync();  // all partials have landed
-    if (tracer) TB_TRACE(7);
-    if (epi) {
-      for (int slot = eh; slot < per; slot += 2) {
-        const int u = slot * S + (int)crank;
-        const int mt = u / CH, c0 = (u % CH) * 32;
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
-        tmem_ld_wait();
-        float v[32];
-        // Partials are added in rank order 0, 1, ..., S-1 whatever the timing.
-        for (int s = 0; s < S; ++s) {
-          if ((uint32_t)s == crank) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = s == 0 ? __uint_as_float(r[j]) : __fadd_rn(v[j], __uint_as_float(r[j]));
-          } else {
-            const int sidx = (uint32_t)s < crank ? s : s - 1;
-            const float4* src = (const float4*)((const unsigned char*)recv + (sidx * per + slot) * UNIT_BYTES) + rit;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 t = src[j * 128];
-              if (s == 0) {
-                v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
-              } else {
-                v[4 * j] = __fadd_rn(v[4 * j], t.x);
-                v[4 * j + 1] = __fadd_rn(v[4 * j + 1], t.y);
-                v[4 * j + 2] = __fadd_rn(v[4 * j + 2], t.z);
-                v[4 * j + 3] = __fadd_rn(v[4 * j + 3], t.w);
-              }
-            }
-          }
-        }
-        store_chunk<EPI>(p, m0 + mt * BM + rit, n0 + c0, v);
-      }
-    }
-  }
   if (tracer) TB_TRACE(8);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+// ---- CTA pairs ------------------------------------------------------------------------
+// With 129 to 256 rows per tile (a decode step), one CTA has to take in its whole activation
+// tile again for every weight tile, and what an SM can take in through TMA is the bound: half of
+// it goes to activations. A CTA PAIR (tcgen05 cta_group::2) halves that share: the two CTAs of a
+// cluster run one MMA of M = 256 together, each keeping only ITS 128 rows of the activation
+// slice and HALF of the weight slice's rows in its own shared memory; the even CTA issues the
+// MMAs, each CTA ends up with its 128 rows of the accumulator in its own tensor memory and runs
+// the same epilogue as above on them. gate_up issues two MMAs per K step (gate and up columns)
+// so that a pair covers BN output columns with 2 BN accumulator columns per CTA.
+template <int BN, int EPI>
+struct PairCfg {
+  static constexpr int NOPS = EPI == EPI_GATE_UP ? 2 : 1;  // weight matrices
+  static constexpr int NBH = BN / 2;                       // rows of each weight slice this CTA loads
+  static constexpr int NB = NOPS * BN;                     // accumulator columns per CTA
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = NOPS * NBH * BK * 2;
+  static constexpr int STAGE = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (196 * 1024) / STAGE > 8 ? 8 : (196 * 1024) / STAGE;
+  static constexpr int TMEM_COLS = NB <= 32 ? 32 : NB <= 64 ? 64 : NB <= 128 ? 128 : NB <= 256 ? 256 : 512;
+  static constexpr int BAR_OFF = STAGES * STAGE;
+  static constexpr int SMEM = BAR_OFF + (2 * STAGES + 1) * 8 + 16 + 1024;
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256 && NB <= 512, "UMMA N (M = 256: a multiple of 16) / TMEM columns");
+  static_assert(NBH % 8 == 0 && STAGE % 1024 == 0, "swizzle atoms are 8 rows of 128 bytes");
+  static_assert(STAGES >= 2, "ring too shallow");
+};
+
+// Grid: (2 x row pairs, column tiles, K splits), cluster (2, 1, splits): cluster rank =
+// (blockIdx.x & 1) + 2 * split. K-major weights only (W [N, K]).
+template <int BN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                     const __grid_constant__ CUtensorMap mapB2, const GemmParams p) {
+  using Cfg = PairCfg<BN, EPI>;
+  constexpr int STAGES = Cfg::STAGES, NBH = Cfg::NBH;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + Cfg::BAR_OFF);  // used in the even CTA only: both CTAs' loads count there
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const uint32_t crank = cluster_ctarank();
+  const uint32_t half = crank & 1u;        // which 128 rows of the pair's 256
+  const uint32_t leader = crank & ~1u;     // cluster rank of the pair's even CTA
+  const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+  const int nk = (p.K + BK - 1) / BK;
+  const int S = p.splits;
+  const int k_begin = (int)((long long)nk * blockIdx.z / S), k_end = (int)((long long)nk * (blockIdx.z + 1) / S);
+  const int niter = k_end - k_begin;
+
+  pdl_launch();
+  if (threadIdx.x == 0) {
+    TB_TRACE(0);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // the partner's barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      prefetch_tmap(&mapA);
+      prefetch_tmap(&mapB);
+      if (EPI == EPI_GATE_UP) prefetch_tmap(&mapB2);
+      TB_TRACE(1);
+      // As in gemm_kernel: weight tiles are requested before waiting for the previous kernel.
+      const int pre = niter < STAGES ? niter : STAGES;
+      auto load_b = [&](int i) {
+        const int s = i % STAGES, kc = (k_begin + i) * BK;
+        unsigned char* b = smem + s * Cfg::STAGE + Cfg::A_BYTES;
+        const uint32_t bar = cluster_map(smem_u32(&full[s]), leader);
+        if (half == 0) mbar_expect_tx(&full[s], 2 * Cfg::STAGE);  // this CTA's tiles and the partner's
+        tma_load_2d_pair(b, &mapB, bar, kc, n0 + (int)half * NBH);
+        if (EPI == EPI_GATE_UP) tma_load_2d_pair(b + NBH * BK * 2, &mapB2, bar, kc, n0 + (int)half * NBH);
+      };
+      for (int i = 0; i < pre; ++i) load_b(i);
+      pdl_wait();
+      for (int i = 0; i < niter; ++i) {
+        const int s = i % STAGES, k = i / STAGES, kc = (k_begin + i) * BK;
+        if (i >= pre) {
+          mbar_wait(&empty[s], (k & 1) ^ 1, p.status, 211);
+          load_b(i);
+        }
+        tma_load_2d_pair(smem + s * Cfg::STAGE, &mapA, cluster_map(smem_u32(&full[s]), leader), kc, m0);
+      }
+    }
+  } else if (warp == 1 && half == 0) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_f16(2 * BM, BN, 0, 0);
+      const uint16_t both = (uint16_t)(3u << leader);
+      for (int i = 0; i < niter; ++i) {
+        const int s = i % STAGES, k = i / STAGES;
+        mbar_wait(&full[s], k & 1, p.status, 212);
+        if (i == 0) TB_TRACE(2);
+        tc_fence_after();
+        const uint32_t a = smem_u32(smem + s * Cfg::STAGE);
+        const uint32_t b = a + Cfg::A_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BK / 16; ++kk) {
+          const uint64_t ad = umma_desc_sw128(a + kk * 32, 16, 1024);
+#pragma unroll
+          for (int op = 0; op < Cfg::NOPS; ++op)
+            umma_f16_pair(tmem + op * BN, ad, umma_desc_sw128(b + op * (NBH * BK * 2) + kk * 32, 16, 1024), idesc,
+                          (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit_pair(&empty[s], both);  // frees the slot in both CTAs once these MMAs have read it
+      }
+      TB_TRACE(3);
+      umma_commit_pair(acc_full, both);
+    }
+  }
+  __syncwarp();
+  tile_epilogue<1, BN, Cfg::NB, EPI>(p, tmem, smem, acc_full, m0, n0, S, crank >> 1, 2u, half);
+  if (warp == 2 && (threadIdx.x & 31) == 0) TB_TRACE(8);
+  // Both CTAs have read their accumulators (and every barrier signal of the pair has landed)
+  // before either frees tensor memory or leaves.
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem, Cfg::TMEM_COLS);
   }
 }
 
@@ -485,6 +638,60 @@ int run(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, co
   return 0;
 }
 
+template <int BN, int EPI>
+int run_pair(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, const void* B2, void* out,
+             bool attr_only) {
+  using Cfg = PairCfg<BN, EPI>;
+  if (attr_only) {
+    TB_CUDA(c, cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    return 0;
+  }
+  CUtensorMap ma, mb, mb2;
+  {
+    const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
+    const uint64_t strides[1] = {(uint64_t)g.K * 2};
+    const uint32_t box[2] = {BK, BM};
+    if (make_tensor_map(c, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return 1;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.N};
+    const uint64_t strides[1] = {(uint64_t)g.K * 2};
+    const uint32_t box[2] = {BK, Cfg::NBH};
+    if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return 1;
+    mb2 = mb;
+    if (EPI == EPI_GATE_UP &&
+        make_tensor_map(c, &mb2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return 1;
+  }
+  GemmParams p;
+  p.out = out;
+  p.M = g.M;
+  p.N = g.N;
+  p.K = g.K;
+  p.splits = splits;
+  p.status = c->status;
+  const dim3 grid(2 * ((g.M + 2 * BM - 1) / (2 * BM)), (g.N + BN - 1) / BN, splits);
+  TB_CUDA(c, launch_kc(c, gemm_pair_kernel<BN, EPI>, grid, dim3(GEMM_THREADS), Cfg::SMEM, 2, splits, ma, mb, mb2, p));
+  return 0;
+}
+
+template <int BN>
+int dispatch_pair(Ctx* c, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
+                  void* out, bool attr_only) {
+  switch (epi_of(kind)) {
+    case EPI_GATE_UP:
+      return run_pair<BN, EPI_GATE_UP>(c, g, splits, A, B, B2, out, attr_only);
+    case EPI_F16:
+      return run_pair<BN, EPI_F16>(c, g, splits, A, B, B2, out, attr_only);
+    case EPI_RESID:
+      return run_pair<BN, EPI_RESID>(c, g, splits, A, B, B2, out, attr_only);
+    default:
+      return run_pair<BN, EPI_F32>(c, g, splits, A, B, B2, out, attr_only);
+  }
+}
+
 template <int EPI, bool B_MN>
 int run_plain(Ctx* c, const GemmShape& g, const void* A, const void* B, const void* B2, void* out) {
   dim3 grid((g.N + 31) / 32, (g.M + 31) / 32);
@@ -517,6 +724,13 @@ int dispatch_epi(Ctx* c, Kind kind, const GemmShape& g, int splits, const void* 
 
 int dispatch(Ctx* c, Kind kind, int mt, int bn, const GemmShape& g, int splits, const void* A, const void* B,
              const void* B2, void* out, bool attr_only) {
+  if (mt == PAIR) {
+    if (kind == K_MATMUL) return fail(c, "gemm: CTA pairs take K-major weights only");
+    if (bn == 128) return dispatch_pair<128>(c, kind, g, splits, A, B, B2, out, attr_only);
+    if (bn == 192) return dispatch_pair<192>(c, kind, g, splits, A, B, B2, out, attr_only);
+    if (bn == 256) return dispatch_pair<256>(c, kind, g, splits, A, B, B2, out, attr_only);
+    return fail(c, "gemm: no such pair tile");
+  }
 #define TB_CASE(MT_, BN_) \
   if (mt == MT_ && bn == BN_) return dispatch_epi<MT_, BN_>(c, kind, g, splits, A, B, B2, out, attr_only);
   TB_CASE(1, 32) TB_CASE(1, 64) TB_CASE(1, 128) TB_CASE(1, 256)
@@ -525,6 +739,7 @@ int dispatch(Ctx* c, Kind kind, int mt, int bn, const GemmShape& g, int splits, 
   return fail(c, "gemm: no such tile");
 }
 
+// mt: 1 or 2 = 128-row accumulators of one CTA; PAIR = a CTA pair on a 256-row tile.
 struct Plan {
   int mt, bn, splits;
   double t;
@@ -536,7 +751,24 @@ struct Plan {
 const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
   const int epi = epi_of(kind);
   const int nk = (g.K + BK - 1) / BK;
-  if (mt != 1 && mt != 2) return "MT is 1 or 2";
+  if (mt == PAIR) {
+    if (kind == K_MATMUL) return "CTA pairs take K-major weights only";
+    if (bn != 128 && bn != 192 && bn != 256) return "pair tiles are 128, 192 or 256 columns wide";
+    const int nops = epi == EPI_GATE_UP ? 2 : 1;
+    const int stage = BM * BK * 2 + nops * (bn / 2) * BK * 2;
+    int stages = (196 * 1024) / stage;
+    if (stages > 8) stages = 8;
+    if (s < 1 || s > 4) return "splits is 1 to 4 with CTA pairs (a cluster of at most 8)";
+    if (s > 1) {
+      const int units = bn / 32;
+      if (epi == EPI_GATE_UP) return "gate_up does not split K";
+      if (s > nk) return "more splits than 64-wide K blocks";
+      if (units % s) return "splits must divide the tile's 128 x 32 units";
+      if ((s - 1) * (units / s) * UNIT_BYTES > stages * stage) return "the partial tiles of the other splits do not fit the ring";
+    }
+    return nullptr;
+  }
+  if (mt != 1 && mt != 2) return "MT is 1, 2 or 3 (3 = a CTA pair on a 256-row tile)";
   if (bn != 32 && bn != 64 && bn != 112 && bn != 128 && bn != 192 && bn != 256) return "BN is 32, 64, 112, 128, 192 or 256";
   if (bn == 112 && (epi != EPI_GATE_UP || mt != 2)) return "the 112-column tile exists for gate_up with MT = 2 only";
   if (bn == 192 && mt != 2) return "the 192-column tile exists with MT = 2 only";
@@ -592,6 +824,28 @@ std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
         const double floor_t = (2.0 * g.M * g.K + 2.0 * nbf * (double)g.N * g.K + (double)out_bytes * g.M * g.N) / HBM;
         if (t < floor_t) t = floor_t;
         all.push_back({mt, bn, s, t});
+      }
+    }
+  }
+  // CTA pairs, for tiles of 129 rows or more: a CTA takes in 128 rows of activations and half
+  // of each weight slice per K step.
+  if (g.M > BM && kind != K_MATMUL) {
+    for (int bn : {256, 192, 128}) {
+      for (int s = 1; s <= 4; s *= 2) {
+        if (plan_error(kind, g, PAIR, bn, s)) continue;
+        if (s > 1 && nk < 8 * s) continue;
+        const int stage = BM * BK * 2 + nbf * (bn / 2) * BK * 2;
+        const long long ctas = 2LL * ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + bn - 1) / bn) * s;
+        const long long waves = (ctas + sms - 1) / sms;
+        const double kiter = (double)((nk + s - 1) / s);
+        const double t_feed = kiter * stage / FEED;
+        const double t_mma = kiter * (2.0 * BM * nbf * bn * BK) / TENSOR;
+        double t_epi = (double)BM * bn * out_bytes / FEED;
+        if (s > 1) t_epi += 2.0e-6 + 2.0 * (s - 1) / s * BM * bn * 4 / FEED;
+        double t = waves * ((t_feed > t_mma ? t_feed : t_mma) + 2.0e-6 + t_epi);
+        const double floor_t = (2.0 * g.M * g.K + 2.0 * nbf * (double)g.N * g.K + (double)out_bytes * g.M * g.N) / HBM;
+        if (t < floor_t) t = floor_t;
+        all.push_back({PAIR, bn, s, t});
       }
     }
   }

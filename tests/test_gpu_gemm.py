@@ -28,6 +28,7 @@ def launch(gpu, name, arrays, out):
 
 SHAPES = [(16, 96, 256), (32, 96, 256), (64, 96, 256),       # tests/llm.rs:118-119
           (16, 512, 128), (256, 6144, 4096), (256, 4096, 512), (100, 200, 72),
+          (256, 768, 4096), (256, 4096, 1792),                # an 8-way tensor-parallel rank's QKV and down_proj
           (128, 256, 64), (129, 264, 200), (300, 40, 1032), (2048, 512, 256), (1, 8, 8)]
 
 
@@ -99,9 +100,14 @@ def test_matmul_4096_cubed(gpu):
     ("2,128,2", 256, 264, 2048), ("2,128,4", 256, 4096, 4096), ("2,192,4", 256, 6144, 4096),
     ("2,256,4", 250, 1288, 4104), ("2,256,2", 256, 1296, 1096), ("1,128,4", 100, 136, 2056),
     ("2,64,4", 256, 200, 3080), ("2,128,4", 256, 4104, 14336),
+    # MT = 3: a CTA pair (tcgen05 cta_group::2) on a 256-row tile, each CTA holding 128 rows of X
+    # and half of the weight slice; alone, with cluster split-K, and over several row pairs.
+    ("3,256,1", 256, 784, 1048), ("3,128,1", 200, 400, 1032), ("3,192,1", 129, 584, 520),
+    ("3,256,2", 256, 1304, 2056), ("3,192,2", 256, 6152, 4096), ("3,256,4", 250, 4112, 4104),
+    ("3,128,4", 256, 272, 2048), ("3,256,1", 600, 528, 512), ("3,128,2", 1000, 136, 1096),
 ])
 def test_forced_tiles_and_cluster_split_k(gpu, plan, M, N, K, monkeypatch):
-    """Every tile shape and the cluster split-K exchange (TB200_GEMM_PLAN = MT,BN,splits), on shapes
+    """Every tile shape, the CTA-pair kernel and the cluster split-K exchange (TB200_GEMM_PLAN = MT,BN,splits), on shapes
     no other test uses (a kernel is made once per shape), for all four epilogues; and the split
     sum is the same bits on every run (partials are added in rank order)."""
     monkeypatch.setenv("TB200_GEMM_PLAN", plan)
