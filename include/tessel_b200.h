@@ -109,6 +109,20 @@ int tb200_kernel(tb200_ctx* ctx, const char* name, const int64_t* shapes, const 
  * restriction. */
 int tb200_launch(tb200_ctx* ctx, tb200_op op, const uint64_t* args, int n_args);
 
+/* Engine::mm (src/llm/engine.rs:233-270), moved behind the boundary because the
+ * tile shapes live here: the candidate tile configurations of a projection
+ * kernel (linear, linear_residual, logits, linear_f32, gate_up, matmul) are
+ * timed on the device, on `args` (the launch arguments of tb200_launch; the
+ * kernel's output is overwritten, or for linear_residual accumulated into,
+ * some tens of times: tune before the step that rewrites it, as the reference
+ * does), with the L2 overwritten between launches, and the fastest is kept for
+ * every later launch of `op`. `plan`, if not NULL, receives the choice as
+ * {MT, BN, splits} (MT 3 = a CTA pair; zeros for a kernel with nothing to
+ * choose), `best_us` its median time. Other kernels: nothing to tune, success.
+ * Not during capture; allocates and frees a 192 MB scratch buffer. With
+ * TB200_GEMM_PLAN set in the environment the forced plan stays. */
+int tb200_tune(tb200_ctx* ctx, tb200_op op, const uint64_t* args, int n_args, int32_t* plan, float* best_us);
+
 /* Gpu::capture_begin / capture_end / replay (src/gpu.rs:233-247). */
 int tb200_capture_begin(tb200_ctx* ctx);
 int tb200_capture_end(tb200_ctx* ctx, tb200_graph* out);
@@ -122,6 +136,21 @@ int tb200_sync(tb200_ctx* ctx);
  * stream around whatever is launched in between; `ms` is device time. */
 int tb200_time_begin(tb200_ctx* ctx);
 int tb200_time_end(tb200_ctx* ctx, float* ms);
+
+/* Gpu::profile, Gpu::phase and Gpu::profile_rows (src/gpu.rs:38-42, :198-222).
+ * tb200_profile(ctx, 1) clears the table and starts profiling: every
+ * tb200_launch (and tb200_allreduce) then waits for its kernel and adds its
+ * device time under (phase, kernel), where kernel is the name followed by the
+ * shape of its last array, e.g. "linear -> [256, 6144]"; launches recorded into
+ * a graph are not timed, so profile with plain launches. tb200_profile(ctx, 0)
+ * stops it (the table stays). tb200_phase names the phase later launches are
+ * counted under ("prefill", "decode"). tb200_profile_rows sorts the table,
+ * largest total first, and returns the number of rows; tb200_profile_row reads
+ * row i (strings valid until the next tb200_profile_rows or tb200_profile). */
+int tb200_profile(tb200_ctx* ctx, int on);
+int tb200_phase(tb200_ctx* ctx, const char* phase);
+int tb200_profile_rows(tb200_ctx* ctx, int* n_rows);
+int tb200_profile_row(tb200_ctx* ctx, int i, const char** phase, const char** kernel, uint64_t* launches, double* ms);
 
 /* Gpu::launches (src/gpu.rs:37): kernels launched through this context
  * (a replayed graph counts every kernel it holds). */

@@ -27,12 +27,18 @@ SYMBOLS = [
     ("tb200_kernel", C.c_int,
      [C.c_void_p, C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_int32)]),
     ("tb200_launch", C.c_int, [C.c_void_p, C.c_int32, _u64p, C.c_int]),
+    ("tb200_tune", C.c_int, [C.c_void_p, C.c_int32, _u64p, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_float)]),
     ("tb200_capture_begin", C.c_int, [C.c_void_p]),
     ("tb200_capture_end", C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     ("tb200_replay", C.c_int, [C.c_void_p, C.c_int32]),
     ("tb200_sync", C.c_int, [C.c_void_p]),
     ("tb200_time_begin", C.c_int, [C.c_void_p]),
     ("tb200_time_end", C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
+    ("tb200_profile", C.c_int, [C.c_void_p, C.c_int]),
+    ("tb200_phase", C.c_int, [C.c_void_p, C.c_char_p]),
+    ("tb200_profile_rows", C.c_int, [C.c_void_p, C.POINTER(C.c_int)]),
+    ("tb200_profile_row", C.c_int,
+     [C.c_void_p, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p), _u64p, C.POINTER(C.c_double)]),
     ("tb200_launch_count", C.c_int, [C.c_void_p, _u64p]),
     ("tb200_set_stream", C.c_int, [C.c_void_p, C.c_void_p]),
     ("tb200_get_stream", C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),

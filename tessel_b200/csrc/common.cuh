@@ -46,6 +46,14 @@ enum Kind : int {
   K_COUNT
 };
 
+// Tensor maps already encoded for an op: they depend only on the op (shapes, tile) and the
+// operand addresses, so a launch that sees the same addresses again (layer l of every step)
+// reuses them instead of calling cuTensorMapEncodeTiled two or three times.
+struct MapEntry {
+  uint64_t key[4];
+  CUtensorMap m[3];
+};
+
 struct Op {
   Kind kind;
   std::string name;
@@ -57,6 +65,21 @@ struct Op {
   size_t scratch_bytes = 0;
   // Kernel-specific tuning chosen when the op is made.
   int p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+  std::vector<MapEntry> maps;
+
+  // The cached maps for `key`, or null; `fresh` returns a slot to fill (the cache is emptied
+  // when it has grown past a few hundred entries: operands that keep changing).
+  const MapEntry* find_maps(const uint64_t key[4]) const {
+    for (const MapEntry& e : maps)
+      if (e.key[0] == key[0] && e.key[1] == key[1] && e.key[2] == key[2] && e.key[3] == key[3]) return &e;
+    return nullptr;
+  }
+  MapEntry* fresh_maps(const uint64_t key[4]) {
+    if (maps.size() >= 512) maps.clear();
+    maps.emplace_back();
+    for (int i = 0; i < 4; ++i) maps.back().key[i] = key[i];
+    return &maps.back();
+  }
 };
 
 struct Ctx {
@@ -85,6 +108,12 @@ struct Ctx {
   // resident (and run their set-up) while this one drains; each kernel waits for its
   // predecessor itself (griddepcontrol.wait) before it touches activations. TB200_PDL=0 turns it off.
   bool pdl = true;
+  // Per-kernel profile (Gpu::profile of src/gpu.rs:38-42): when on, every launch waits for its
+  // kernel and adds its device time under (phase, kernel).
+  bool profiling = false;
+  std::string phase;
+  std::map<std::pair<std::string, std::string>, std::pair<uint64_t, double>> profile;
+  std::vector<std::pair<std::pair<std::string, std::string>, std::pair<uint64_t, double>>> profile_sorted;
 };
 
 int fail(Ctx* c, const std::string& msg);
@@ -107,6 +136,7 @@ int make_glue(Ctx* c, Op& op);
 int launch_glue(Ctx* c, Op& op, const uint64_t* a);
 int make_gemm(Ctx* c, Op& op);
 int launch_gemm(Ctx* c, Op& op, const uint64_t* a);
+int tune_gemm(Ctx* c, Op& op, const uint64_t* a, float* best_us);
 int make_decode(Ctx* c, Op& op);
 int launch_decode(Ctx* c, Op& op, const uint64_t* a);
 int make_prefill(Ctx* c, Op& op);

@@ -3,6 +3,7 @@
 #include <dlfcn.h>
 #include <string.h>
 
+#include <algorithm>
 #include <sstream>
 
 #include "../../include/tessel_b200.h"
@@ -86,6 +87,26 @@ static const KindInfo KINDS[] = {
     {"argmax_partial", K_ARGMAX_PARTIAL, 2, 4},
     {"argmax_merge", K_ARGMAX_MERGE, 2, 2},
 };
+
+static std::string shape_text(const std::vector<int64_t>& s) {
+  std::ostringstream o;
+  o << "[";
+  for (size_t i = 0; i < s.size(); ++i) o << (i ? ", " : "") << s[i];
+  o << "]";
+  return o.str();
+}
+
+// Closes the event pair opened before a profiled launch and books its time under (phase, kernel).
+static int profile_add(Ctx* c, const std::string& kernel) {
+  float ms = 0.f;
+  TB_CUDA(c, cudaEventRecord(c->ev1, c->stream));
+  TB_CUDA(c, cudaEventSynchronize(c->ev1));
+  TB_CUDA(c, cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+  auto& e = c->profile[{c->phase, kernel}];
+  e.first += 1;
+  e.second += ms;
+  return 0;
+}
 
 static bool is_gemm(Kind k) {
   return k == K_LINEAR || k == K_LINEAR_RESIDUAL || k == K_LOGITS || k == K_GATE_UP || k == K_MATMUL ||
@@ -324,6 +345,8 @@ int tb200_launch(tb200_ctx* h, tb200_op id, const uint64_t* args, int n_args) {
     return fail(c, s.str());
   }
   if (!args) return fail(c, "tb200_launch: args is NULL");
+  const bool timed = c->profiling && !c->capturing;
+  if (timed) TB_CUDA(c, cudaEventRecord(c->ev0, c->stream));
   int r;
   if (is_gemm(op.kind))
     r = launch_gemm(c, op, args);
@@ -335,6 +358,26 @@ int tb200_launch(tb200_ctx* h, tb200_op id, const uint64_t* args, int n_args) {
     r = launch_tp(c, op, args);
   else
     r = launch_glue(c, op, args);
+  if (r || !timed) return r;
+  return profile_add(c, op.name + " -> " + shape_text(op.shapes.empty() ? std::vector<int64_t>() : op.shapes.back()));
+}
+
+int tb200_tune(tb200_ctx* h, tb200_op id, const uint64_t* args, int n_args, int32_t* plan, float* best_us) {
+  Ctx* c = &h->c;
+  if (id < 0 || (size_t)id >= c->ops.size()) return fail(c, "tb200_tune: no such kernel handle");
+  Op& op = c->ops[id];
+  if (n_args != op.n_args || !args) return fail(c, op.name + ": tb200_tune takes the kernel's launch arguments");
+  if (best_us) *best_us = 0.f;
+  int r = 0;
+  if (is_gemm(op.kind)) {
+    TB_CUDA(c, cudaSetDevice(c->device));
+    r = tune_gemm(c, op, args, best_us);
+  }
+  if (plan) {
+    plan[0] = is_gemm(op.kind) && op.p0 == 1 ? op.p1 : 0;
+    plan[1] = is_gemm(op.kind) && op.p0 == 1 ? op.p2 : 0;
+    plan[2] = is_gemm(op.kind) && op.p0 == 1 ? op.p3 : 0;
+  }
   return r;
 }
 
@@ -397,6 +440,42 @@ int tb200_time_end(tb200_ctx* h, float* ms) {
   TB_CUDA(c, cudaEventRecord(c->ev1, c->stream));
   TB_CUDA(c, cudaEventSynchronize(c->ev1));
   TB_CUDA(c, cudaEventElapsedTime(ms, c->ev0, c->ev1));
+  return 0;
+}
+
+int tb200_profile(tb200_ctx* h, int on) {
+  Ctx* c = &h->c;
+  if (c->capturing) return fail(c, "tb200_profile during capture");
+  if (on) {
+    c->profile.clear();
+    c->profile_sorted.clear();
+  }
+  c->profiling = on != 0;
+  return 0;
+}
+
+int tb200_phase(tb200_ctx* h, const char* phase) {
+  h->c.phase = phase ? phase : "";
+  return 0;
+}
+
+int tb200_profile_rows(tb200_ctx* h, int* n_rows) {
+  Ctx* c = &h->c;
+  c->profile_sorted.assign(c->profile.begin(), c->profile.end());
+  std::stable_sort(c->profile_sorted.begin(), c->profile_sorted.end(),
+                   [](const auto& a, const auto& b) { return a.second.second > b.second.second; });
+  if (n_rows) *n_rows = (int)c->profile_sorted.size();
+  return 0;
+}
+
+int tb200_profile_row(tb200_ctx* h, int i, const char** phase, const char** kernel, uint64_t* launches, double* ms) {
+  Ctx* c = &h->c;
+  if (i < 0 || (size_t)i >= c->profile_sorted.size()) return fail(c, "tb200_profile_row: no such row (call tb200_profile_rows first)");
+  const auto& r = c->profile_sorted[i];
+  if (phase) *phase = r.first.first.c_str();
+  if (kernel) *kernel = r.first.second.c_str();
+  if (launches) *launches = r.second.first;
+  if (ms) *ms = r.second.second;
   return 0;
 }
 
@@ -489,9 +568,16 @@ int tb200_allreduce(tb200_ctx* h, uint64_t dptr, size_t count, int dtype) {
   NcclAllReduce f = (NcclAllReduce)dlsym(c->nccl_lib, "ncclAllReduce");
   if (!f) return fail(c, "ncclAllReduce not found");
   const int nccl_f32 = 7, nccl_f16 = 6, nccl_sum = 0;
+  const bool timed = c->profiling && !c->capturing;
+  if (timed) TB_CUDA(c, cudaEventRecord(c->ev0, c->stream));
   int r = f((const void*)dptr, (void*)dptr, count, dtype == 0 ? nccl_f32 : nccl_f16, nccl_sum, c->comm, c->stream);
   if (r) return nccl_fail(c, r, "ncclAllReduce");
   c->launches += 1;
+  if (timed) {
+    std::ostringstream o;
+    o << "allreduce -> [" << count << "]";
+    return profile_add(c, o.str());
+  }
   return 0;
 }
 

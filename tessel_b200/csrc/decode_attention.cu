@@ -460,17 +460,25 @@ int launch_decode(Ctx* c, Op& op, const uint64_t* a) {
     return 0;
   }
   // [NP, P, G, D] seen as (64 | D/64 * G | P | NP): a (page, kv head) tile is D/64 boxes of 16 rows x 128 bytes.
-  const int SUB = d.D / 64;
-  CUtensorMap mk, mv;
-  const uint64_t dims[4] = {64, (uint64_t)SUB * d.G, (uint64_t)d.P, (uint64_t)d.NP};
-  const uint64_t strides[3] = {128, (uint64_t)d.G * d.D * 2, (uint64_t)d.P * d.G * d.D * 2};
-  const uint32_t box[4] = {64, 1, 16, 1};
-  if (make_tensor_map(c, &mk, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (const void*)a[1], dims, strides, box,
-                      CU_TENSOR_MAP_SWIZZLE_128B))
-    return 1;
-  if (make_tensor_map(c, &mv, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (const void*)a[2], dims, strides, box,
-                      CU_TENSOR_MAP_SWIZZLE_128B))
-    return 1;
+  const uint64_t key[4] = {a[1], a[2], 0, 0};
+  const MapEntry* hit = op.find_maps(key);
+  if (!hit) {
+    const int SUB = d.D / 64;
+    const uint64_t dims[4] = {64, (uint64_t)SUB * d.G, (uint64_t)d.P, (uint64_t)d.NP};
+    const uint64_t strides[3] = {128, (uint64_t)d.G * d.D * 2, (uint64_t)d.P * d.G * d.D * 2};
+    const uint32_t box[4] = {64, 1, 16, 1};
+    CUtensorMap k4, v4;
+    if (make_tensor_map(c, &k4, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (const void*)a[1], dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B))
+      return 1;
+    if (make_tensor_map(c, &v4, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, (const void*)a[2], dims, strides, box,
+                        CU_TENSOR_MAP_SWIZZLE_128B))
+      return 1;
+    MapEntry* e = op.fresh_maps(key);
+    e->m[0] = k4, e->m[1] = v4;
+    hit = e;
+  }
+  const CUtensorMap &mk = hit->m[0], &mv = hit->m[1];
   DecodeParams p;
   p.Q = (const __half*)a[0];
   p.table = (const int*)a[3];

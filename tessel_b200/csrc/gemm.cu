@@ -588,7 +588,7 @@ int epi_of(Kind k) {
 }
 
 template <int MT, int BN, int EPI, bool B_MN>
-int run(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, const void* B2, void* out,
+int run(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, const void* B, const void* B2, void* out,
         bool attr_only) {
   using Cfg = GemmCfg<MT, BN, EPI>;
   if (attr_only) {
@@ -596,36 +596,44 @@ int run(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, co
                                     Cfg::SMEM));
     return 0;
   }
-  CUtensorMap ma, mb, mb2;
-  {
-    const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
-    const uint64_t strides[1] = {(uint64_t)g.K * 2};
-    const uint32_t box[2] = {BK, MT * BM};
-    if (make_tensor_map(c, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B))
-      return 1;
+  const uint64_t key[4] = {(uint64_t)A, (uint64_t)B, (uint64_t)B2, ((uint64_t)MT << 32) | ((uint64_t)BN << 8) | (uint64_t)splits};
+  const MapEntry* hit = op.find_maps(key);
+  if (!hit) {
+    CUtensorMap ma, mb, mb2;
+    {
+      const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
+      const uint64_t strides[1] = {(uint64_t)g.K * 2};
+      const uint32_t box[2] = {BK, MT * BM};
+      if (make_tensor_map(c, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B))
+        return 1;
+    }
+    if (B_MN) {
+      const uint64_t dims[2] = {(uint64_t)g.N, (uint64_t)g.K};
+      const uint64_t strides[1] = {(uint64_t)g.N * 2};
+      const uint32_t box[2] = {64, BK};
+      if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B))
+        return 1;
+      mb2 = mb;
+    } else {
+      const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.N};
+      const uint64_t strides[1] = {(uint64_t)g.K * 2};
+      const uint32_t box[2] = {BK, BN};
+      if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B))
+        return 1;
+      mb2 = mb;
+      if (EPI == EPI_GATE_UP &&
+          make_tensor_map(c, &mb2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B2, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B))
+        return 1;
+    }
+    MapEntry* e = op.fresh_maps(key);
+    e->m[0] = ma, e->m[1] = mb, e->m[2] = mb2;
+    hit = e;
   }
-  if (B_MN) {
-    const uint64_t dims[2] = {(uint64_t)g.N, (uint64_t)g.K};
-    const uint64_t strides[1] = {(uint64_t)g.N * 2};
-    const uint32_t box[2] = {64, BK};
-    if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B))
-      return 1;
-    mb2 = mb;
-  } else {
-    const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.N};
-    const uint64_t strides[1] = {(uint64_t)g.K * 2};
-    const uint32_t box[2] = {BK, BN};
-    if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B))
-      return 1;
-    mb2 = mb;
-    if (EPI == EPI_GATE_UP &&
-        make_tensor_map(c, &mb2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B2, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B))
-      return 1;
-  }
+  const CUtensorMap &ma = hit->m[0], &mb = hit->m[1], &mb2 = hit->m[2];
   GemmParams p;
   p.out = out;
   p.M = g.M;
@@ -639,32 +647,40 @@ int run(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, co
 }
 
 template <int BN, int EPI>
-int run_pair(Ctx* c, const GemmShape& g, int splits, const void* A, const void* B, const void* B2, void* out,
+int run_pair(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, const void* B, const void* B2, void* out,
              bool attr_only) {
   using Cfg = PairCfg<BN, EPI>;
   if (attr_only) {
     TB_CUDA(c, cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     return 0;
   }
-  CUtensorMap ma, mb, mb2;
-  {
-    const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
-    const uint64_t strides[1] = {(uint64_t)g.K * 2};
-    const uint32_t box[2] = {BK, BM};
-    if (make_tensor_map(c, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
-      return 1;
+  const uint64_t key[4] = {(uint64_t)A, (uint64_t)B, (uint64_t)B2, ((uint64_t)PAIR << 32) | ((uint64_t)BN << 8) | (uint64_t)splits};
+  const MapEntry* hit = op.find_maps(key);
+  if (!hit) {
+    CUtensorMap ma, mb, mb2;
+    {
+      const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
+      const uint64_t strides[1] = {(uint64_t)g.K * 2};
+      const uint32_t box[2] = {BK, BM};
+      if (make_tensor_map(c, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+        return 1;
+    }
+    {
+      const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.N};
+      const uint64_t strides[1] = {(uint64_t)g.K * 2};
+      const uint32_t box[2] = {BK, Cfg::NBH};
+      if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+        return 1;
+      mb2 = mb;
+      if (EPI == EPI_GATE_UP &&
+          make_tensor_map(c, &mb2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+        return 1;
+    }
+    MapEntry* e = op.fresh_maps(key);
+    e->m[0] = ma, e->m[1] = mb, e->m[2] = mb2;
+    hit = e;
   }
-  {
-    const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.N};
-    const uint64_t strides[1] = {(uint64_t)g.K * 2};
-    const uint32_t box[2] = {BK, Cfg::NBH};
-    if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
-      return 1;
-    mb2 = mb;
-    if (EPI == EPI_GATE_UP &&
-        make_tensor_map(c, &mb2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
-      return 1;
-  }
+  const CUtensorMap &ma = hit->m[0], &mb = hit->m[1], &mb2 = hit->m[2];
   GemmParams p;
   p.out = out;
   p.M = g.M;
@@ -678,17 +694,17 @@ int run_pair(Ctx* c, const GemmShape& g, int splits, const void* A, const void* 
 }
 
 template <int BN>
-int dispatch_pair(Ctx* c, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
+int dispatch_pair(Ctx* c, Op& op, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
                   void* out, bool attr_only) {
   switch (epi_of(kind)) {
     case EPI_GATE_UP:
-      return run_pair<BN, EPI_GATE_UP>(c, g, splits, A, B, B2, out, attr_only);
+      return run_pair<BN, EPI_GATE_UP>(c, op, g, splits, A, B, B2, out, attr_only);
     case EPI_F16:
-      return run_pair<BN, EPI_F16>(c, g, splits, A, B, B2, out, attr_only);
+      return run_pair<BN, EPI_F16>(c, op, g, splits, A, B, B2, out, attr_only);
     case EPI_RESID:
-      return run_pair<BN, EPI_RESID>(c, g, splits, A, B, B2, out, attr_only);
+      return run_pair<BN, EPI_RESID>(c, op, g, splits, A, B, B2, out, attr_only);
     default:
-      return run_pair<BN, EPI_F32>(c, g, splits, A, B, B2, out, attr_only);
+      return run_pair<BN, EPI_F32>(c, op, g, splits, A, B, B2, out, attr_only);
   }
 }
 
@@ -703,36 +719,36 @@ int run_plain(Ctx* c, const GemmShape& g, const void* A, const void* B, const vo
 
 // The instantiated tiles. gate_up: BN <= 128 (its MMA is 2 BN wide); matmul: BN >= 64.
 template <int MT, int BN>
-int dispatch_epi(Ctx* c, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
+int dispatch_epi(Ctx* c, Op& op, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
                  void* out, bool attr_only) {
   const int epi = epi_of(kind);
   if constexpr (BN == 112) {
-    if (epi == EPI_GATE_UP) return run<MT, BN, EPI_GATE_UP, false>(c, g, splits, A, B, B2, out, attr_only);
+    if (epi == EPI_GATE_UP) return run<MT, BN, EPI_GATE_UP, false>(c, op, g, splits, A, B, B2, out, attr_only);
   } else if (kind == K_MATMUL) {
-    if constexpr (BN >= 64 && BN != 192) return run<MT, BN, EPI_F16, true>(c, g, splits, A, B, B2, out, attr_only);
+    if constexpr (BN >= 64 && BN != 192) return run<MT, BN, EPI_F16, true>(c, op, g, splits, A, B, B2, out, attr_only);
   } else if (epi == EPI_GATE_UP) {
-    if constexpr (BN <= 128) return run<MT, BN, EPI_GATE_UP, false>(c, g, splits, A, B, B2, out, attr_only);
+    if constexpr (BN <= 128) return run<MT, BN, EPI_GATE_UP, false>(c, op, g, splits, A, B, B2, out, attr_only);
   } else if (epi == EPI_F16) {
-    return run<MT, BN, EPI_F16, false>(c, g, splits, A, B, B2, out, attr_only);
+    return run<MT, BN, EPI_F16, false>(c, op, g, splits, A, B, B2, out, attr_only);
   } else if (epi == EPI_RESID) {
-    return run<MT, BN, EPI_RESID, false>(c, g, splits, A, B, B2, out, attr_only);
+    return run<MT, BN, EPI_RESID, false>(c, op, g, splits, A, B, B2, out, attr_only);
   } else {
-    return run<MT, BN, EPI_F32, false>(c, g, splits, A, B, B2, out, attr_only);
+    return run<MT, BN, EPI_F32, false>(c, op, g, splits, A, B, B2, out, attr_only);
   }
   return fail(c, "gemm: tile not instantiated for this kernel");
 }
 
-int dispatch(Ctx* c, Kind kind, int mt, int bn, const GemmShape& g, int splits, const void* A, const void* B,
+int dispatch(Ctx* c, Op& op, Kind kind, int mt, int bn, const GemmShape& g, int splits, const void* A, const void* B,
              const void* B2, void* out, bool attr_only) {
   if (mt == PAIR) {
     if (kind == K_MATMUL) return fail(c, "gemm: CTA pairs take K-major weights only");
-    if (bn == 128) return dispatch_pair<128>(c, kind, g, splits, A, B, B2, out, attr_only);
-    if (bn == 192) return dispatch_pair<192>(c, kind, g, splits, A, B, B2, out, attr_only);
-    if (bn == 256) return dispatch_pair<256>(c, kind, g, splits, A, B, B2, out, attr_only);
+    if (bn == 128) return dispatch_pair<128>(c, op, kind, g, splits, A, B, B2, out, attr_only);
+    if (bn == 192) return dispatch_pair<192>(c, op, kind, g, splits, A, B, B2, out, attr_only);
+    if (bn == 256) return dispatch_pair<256>(c, op, kind, g, splits, A, B, B2, out, attr_only);
     return fail(c, "gemm: no such pair tile");
   }
 #define TB_CASE(MT_, BN_) \
-  if (mt == MT_ && bn == BN_) return dispatch_epi<MT_, BN_>(c, kind, g, splits, A, B, B2, out, attr_only);
+  if (mt == MT_ && bn == BN_) return dispatch_epi<MT_, BN_>(c, op, kind, g, splits, A, B, B2, out, attr_only);
   TB_CASE(1, 32) TB_CASE(1, 64) TB_CASE(1, 128) TB_CASE(1, 256)
   TB_CASE(2, 32) TB_CASE(2, 64) TB_CASE(2, 112) TB_CASE(2, 128) TB_CASE(2, 192) TB_CASE(2, 256)
 #undef TB_CASE
@@ -827,11 +843,13 @@ std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
       }
     }
   }
-  // CTA pairs, for tiles of 129 rows or more: a CTA takes in 128 rows of activations and half
-  // of each weight slice per K step.
-  if (g.M > BM && kind != K_MATMUL) {
+  // CTA pairs, for one tile of 129 to 256 rows (a decode step), where they were measured: a CTA
+  // takes in 128 rows of activations and half of each weight slice per K step. Clusters of
+  // eight (a pair times four splits) measured 40-50 % slower than two splits at every decode
+  // shape, so they are left to a forced plan.
+  if (g.M > BM && g.M <= 2 * BM && kind != K_MATMUL) {
     for (int bn : {256, 192, 128}) {
-      for (int s = 1; s <= 4; s *= 2) {
+      for (int s = 1; s <= 2; s *= 2) {
         if (plan_error(kind, g, PAIR, bn, s)) continue;
         if (s > 1 && nk < 8 * s) continue;
         const int stage = BM * BK * 2 + nbf * (bn / 2) * BK * 2;
@@ -894,8 +912,22 @@ int make_gemm(Ctx* c, Op& op) {
   op.p1 = pl.mt;
   op.p2 = pl.bn;
   op.p3 = pl.splits;
-  return dispatch(c, op.kind, pl.mt, pl.bn, g, pl.splits, nullptr, nullptr, nullptr, nullptr, true);
+  return dispatch(c, op, op.kind, pl.mt, pl.bn, g, pl.splits, nullptr, nullptr, nullptr, nullptr, true);
 }
+
+namespace {
+
+// One launch of `op` with plan (mt, bn, splits) on the launch arguments `a`.
+int launch_plan(Ctx* c, Op& op, const uint64_t* a, int mt, int bn, int splits) {
+  const GemmShape g = gemm_shape(op);
+  const void* A = (const void*)a[0];
+  const void* B = (const void*)a[1];
+  const void* B2 = op.kind == K_GATE_UP ? (const void*)a[2] : nullptr;
+  void* out = (void*)a[op.kind == K_GATE_UP ? 3 : 2];
+  return dispatch(c, op, op.kind, mt, bn, g, splits, A, B, B2, out, false);
+}
+
+}  // namespace
 
 int launch_gemm(Ctx* c, Op& op, const uint64_t* a) {
   if (op.p0 < 0) return 0;
@@ -926,10 +958,72 @@ int launch_gemm(Ctx* c, Op& op, const uint64_t* a) {
     else
       r = run_plain<EPI_GATE_UP, false>(c, g, A, B, B2, out);
   } else {
-    r = dispatch(c, op.kind, op.p1, op.p2, g, op.p3, A, B, B2, out, false);
+    r = launch_plan(c, op, a, op.p1, op.p2, op.p3);
   }
   if (r) return r;
   c->launches += 1;
+  return 0;
+}
+
+// Engine::mm of the reference (src/llm/engine.rs:233-270): the candidate tiles of a projection
+// are timed on the device, on the caller's own buffers, and the fastest is kept for every later
+// launch of the op. Here the candidates are the cost model's best few (single-CTA tiles, CTA
+// pairs, cluster split-K); each is warmed up and then timed launch by launch with the L2
+// overwritten in between, because in a decode step the weights always come from HBM while a
+// back-to-back loop would serve the smaller projections from the 126 MB L2.
+int tune_gemm(Ctx* c, Op& op, const uint64_t* a, float* best_us) {
+  if (best_us) *best_us = 0.f;
+  if (op.p0 != 1 || getenv("TB200_GEMM_PLAN")) return 0;  // nothing to choose, or the choice is forced
+  if (c->capturing) return fail(c, "tb200_tune during graph capture");
+  const GemmShape g = gemm_shape(op);
+  if (g.K == 0) return 0;
+  std::vector<Plan> cands = plan_gemm(op.kind, g, c->sm_count);
+  if (cands.size() > 8) cands.resize(8);
+  const size_t flush_bytes = (size_t)192 << 20;
+  void* flush = nullptr;
+  TB_CUDA(c, cudaMalloc(&flush, flush_bytes));
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  const int WARM = 2, ITERS = 5;
+  float best = 1e30f;
+  Plan pick = {op.p1, op.p2, op.p3, 0.0};
+  int rc = 0;
+  for (const Plan& pl : cands) {
+    if (dispatch(c, op, op.kind, pl.mt, pl.bn, g, pl.splits, nullptr, nullptr, nullptr, nullptr, true)) continue;
+    float times[ITERS];
+    bool ok = true;
+    for (int it = 0; it < WARM + ITERS && ok; ++it) {
+      ok = cudaMemsetAsync(flush, it, flush_bytes, c->stream) == cudaSuccess;
+      ok = ok && cudaEventRecord(e0, c->stream) == cudaSuccess;
+      ok = ok && launch_plan(c, op, a, pl.mt, pl.bn, pl.splits) == 0;
+      ok = ok && cudaEventRecord(e1, c->stream) == cudaSuccess;
+      ok = ok && cudaEventSynchronize(e1) == cudaSuccess;
+      float ms = 0.f;
+      ok = ok && cudaEventElapsedTime(&ms, e0, e1) == cudaSuccess;
+      if (ok && it >= WARM) times[it - WARM] = ms;
+    }
+    if (!ok) {
+      rc = cuda_fail(c, cudaGetLastError(), "tb200_tune");
+      break;
+    }
+    c->launches += WARM + ITERS;
+    std::sort(times, times + ITERS);
+    const float med = times[ITERS / 2];
+    if (med < best) {
+      best = med;
+      pick = pl;
+    }
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaStreamSynchronize(c->stream);
+  cudaFree(flush);
+  if (rc) return rc;
+  op.p1 = pick.mt;
+  op.p2 = pick.bn;
+  op.p3 = pick.splits;
+  if (best_us && best < 1e29f) *best_us = best * 1000.f;
   return 0;
 }
 

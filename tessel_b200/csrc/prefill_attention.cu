@@ -448,8 +448,10 @@ FaShape fa_shape(const Op& op) {
 }
 
 template <int D>
-int run_fa(Ctx* c, const FaShape& f, const void* Q, const void* K, const void* V, const int* starts, void* O,
+int run_fa(Ctx* c, Op& op, const FaShape& f, const void* Q, const void* K, const void* V, const int* starts, void* O,
            float scale) {
+  const uint64_t key[4] = {(uint64_t)Q, (uint64_t)K, (uint64_t)V, 0};
+  const MapEntry* hit = op.find_maps(key);
   CUtensorMap mq, mk, mv;
   auto mk_map = [&](CUtensorMap* m, const void* base, int heads) {
     if (f.plain) {
@@ -465,7 +467,13 @@ int run_fa(Ctx* c, const FaShape& f, const void* Q, const void* K, const void* V
     return make_tensor_map(c, m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box,
                            CU_TENSOR_MAP_SWIZZLE_128B);
   };
-  if (mk_map(&mq, Q, f.H) || mk_map(&mk, K, f.G) || mk_map(&mv, V, f.G)) return 1;
+  if (hit) {
+    mq = hit->m[0], mk = hit->m[1], mv = hit->m[2];
+  } else {
+    if (mk_map(&mq, Q, f.H) || mk_map(&mk, K, f.G) || mk_map(&mv, V, f.G)) return 1;
+    MapEntry* e = op.fresh_maps(key);
+    e->m[0] = mq, e->m[1] = mk, e->m[2] = mv;
+  }
   FaParams p;
   p.starts = starts;
   p.O = (__half*)O;
@@ -515,7 +523,7 @@ int launch_prefill(Ctx* c, Op& op, const uint64_t* a) {
   const float scale = bits_f32(a[f.plain ? 4 : 5]);
   int r;
   if (op.p0) {
-    r = f.D == 128 ? run_fa<128>(c, f, Q, K, V, starts, O, scale) : run_fa<64>(c, f, Q, K, V, starts, O, scale);
+    r = f.D == 128 ? run_fa<128>(c, op, f, Q, K, V, starts, O, scale) : run_fa<64>(c, op, f, Q, K, V, starts, O, scale);
   } else {
     const long long warps = (long long)f.S * f.H;
     TB_CUDA(c, launch_k(c, fa_generic_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, 1, (const __half*)Q, (const __half*)K,

@@ -139,6 +139,12 @@ class Engine:
         self.full_cfg = full
         self.lim = lim
         self.rank, self.nranks = rank, nranks
+        # Time the candidate tiles of each projection on the device the first time a step size is
+        # seen and keep the fastest (src/llm/engine.rs:52, :233-270), for steps of at most
+        # ``tune_rows`` rows: decode steps are what is replayed thousands of times, while every
+        # new prompt length would pay for a tuning pass of its own.
+        self.tune = True
+        self.tune_rows = 256
         # Replay decode steps as CUDA graphs (one launch instead of hundreds).
         self.graphs = True
         self._graph: Dict[tuple, int] = {}
@@ -270,7 +276,8 @@ class Engine:
         g = self.gpu
         g.phase = "prefill" if prefill else "decode"
         # Profiling times every launch on its own, so it runs without graphs.
-        if (not prefill) and self.graphs and g.profile is None and bw == t:
+        profiling = g._profiling if hasattr(g, "_profiling") else g.profile is not None
+        if (not prefill) and self.graphs and not profiling and bw == t:
             # A decode step of this size: replay its recorded launches, or run
             # them and record them for the next time.
             key = (t, greedy, self.fused)
@@ -347,6 +354,18 @@ class Engine:
         return out
 
     # -- the launch sequence -------------------------------------------------------
+    def _mm(self, name: str, shapes, args, t: int) -> K:
+        """The projection kernel ``name`` for these shapes; the first time (on a device that can),
+        its tile candidates are timed on ``args`` - the engine's own buffers with layer 0's
+        weights; anything they write, the step rewrites - and the fastest is kept
+        (``Engine::mm``, src/llm/engine.rs:233-270)."""
+        g = self.gpu
+        kern = g.kernel(name, shapes)
+        tuned = getattr(g, "tuned", None)
+        if self.tune and t <= self.tune_rows and tuned is not None and kern.id not in tuned:
+            tuned[kern.id] = g.tune(kern, args)
+        return kern
+
     def launch_all(self, t: int, prefill: bool, bw: Optional[int], greedy: bool = False) -> None:
         """Launches one step's kernels for ``t`` rows: the decoder, then, for ``bw`` rows of
         logits, the final norm and the LM head (and the token choice when ``greedy``)."""
@@ -360,7 +379,8 @@ class Engine:
         k = g.kernel
         embed = k("embed", [[t], [v, dm], [t, dm]])
         norm = k("rmsnorm", [[t, dm], [dm], [t, dm]])
-        qkv = k("linear", [[t, dm], [w, dm], [t, w]])
+        l0 = self.layers[0]
+        qkv = self._mm("linear", [[t, dm], [w, dm], [t, w]], [self.h, l0.wqkv, self.qkv], t)
         # rope_q and kv_write of the reference (src/llm/engine.rs:391-418) run as one launch.
         ropekv = k("rope_kv", [[t, w], [t], [t], [npos, hd // 2], [npos, hd // 2], [t, nh, hd], [ns, ng, hd],
                                [ns, ng, hd], [t, ng, hd], [t, ng, hd]])
@@ -370,9 +390,10 @@ class Engine:
             att = k("decode_attention", [[t, nh, hd], [lim.pages, lim.page, ng, hd], [lim.pages, lim.page, ng, hd],
                                          [t, mp], [t], [t, nh, hd]])
         proj = "linear_f32" if tp else "linear_residual"
-        oproj = k(proj, [[t, nh * hd], [dm, nh * hd], [t, dm]])
-        gu = k("gate_up", [[t, dm], [f, dm], [f, dm], [t, f]])
-        down = k(proj, [[t, f], [dm, f], [t, dm]])
+        acc = self.part if tp else self.x
+        oproj = self._mm(proj, [[t, nh * hd], [dm, nh * hd], [t, dm]], [self.o, l0.wo, acc], t)
+        gu = self._mm("gate_up", [[t, dm], [f, dm], [f, dm], [t, f]], [self.h, l0.wg, l0.wu, self.mlp], t)
+        down = self._mm(proj, [[t, f], [dm, f], [t, dm]], [self.mlp, l0.wd, acc], t)
         radd = k("residual_add", [[t, dm], [t, dm]]) if tp else None
 
         def project(kern: K, x: Buf, wt: Buf) -> None:
@@ -431,17 +452,23 @@ class Engine:
         if bw is None:
             return
         fin = k("rmsnorm_rows", [[t, dm], [bw], [dm], [bw, dm]])
-        head = k("logits", [[bw, dm], [v, dm], [bw, v]])
         g.launch(fin, [self.x, self.idx, self.norm, self.last, eps])
         if greedy and self.vocab_parallel:
             from .gpu import I32
             r, n = self.rank, self.nranks
             vs = v // n
-            g.launch(k("logits", [[bw, dm], [vs, dm], [bw, vs]]), [self.last, self.head_slice, self.logits])
+            part = self._mm("logits", [[bw, dm], [vs, dm], [bw, vs]], [self.last, self.head_slice, self.logits], bw)
+            g.launch(part, [self.last, self.head_slice, self.logits])
             g.launch(k("argmax_partial", [[bw, vs], [n, bw, 2]]), [self.logits, self.pairs, I32(r), I32(r * vs)])
             g.allreduce(self.pairs, n * bw * 2, 0)
             g.launch(k("argmax_merge", [[n, bw, 2], [bw]]), [self.pairs, self.picked])
             return
+        # Under tensor parallelism every rank computes these logits from the same x and the host
+        # picks from its own copy: the ranks must run the same tile, so this one is not tuned.
+        if self.nranks == 1:
+            head = self._mm("logits", [[bw, dm], [v, dm], [bw, v]], [self.last, self.head, self.logits], bw)
+        else:
+            head = k("logits", [[bw, dm], [v, dm], [bw, v]])
         g.launch(head, [self.last, self.head, self.logits])
         if greedy:
             pick = k("argmax_rows", [[bw, v], [bw]])

@@ -71,11 +71,10 @@ class Gpu:
         self._h = h
         self.device = device
         self.launches = 0
-        # When set, every launch waits for its kernel and adds its time here,
-        # by (phase, kernel): [launches, milliseconds] (src/gpu.rs:38-40).
-        self.profile: Optional[Dict[Tuple[str, str], List[float]]] = None
-        self.phase = ""
-        self._names: Dict[int, str] = {}
+        self._profiling = False
+        self._phase = ""
+        # Kernels whose tiles were chosen by timing (``tune``): id -> ((MT, BN, splits), microseconds).
+        self.tuned: Dict[int, tuple] = {}
 
     # -- plumbing --------------------------------------------------------------
     def _check(self, rc: int) -> None:
@@ -170,24 +169,48 @@ class Gpu:
         ra = (C.c_int32 * max(len(ranks), 1))(*ranks)
         out = C.c_int32()
         self._check(self._l.tb200_kernel(self._h, name.encode(), fa, ra, len(ranks), C.byref(out)))
-        last = list(shapes[-1]) if shapes else []
-        self._names[out.value] = f"{name} -> {last}"
         return K(out.value, name)
 
     def launch(self, k: K, args: Sequence[Arg]) -> None:
         """Launches ``k`` (asynchronously)."""
         raw = (C.c_uint64 * max(len(args), 1))(*[_bits(a) for a in args])
         self.launches += 1
-        if self.profile is None:
-            self._check(self._l.tb200_launch(self._h, k.id, raw, len(args)))
-            return
-        self._check(self._l.tb200_time_begin(self._h))
         self._check(self._l.tb200_launch(self._h, k.id, raw, len(args)))
-        ms = C.c_float()
-        self._check(self._l.tb200_time_end(self._h, C.byref(ms)))
-        e = self.profile.setdefault((self.phase, self._names[k.id]), [0, 0.0])
-        e[0] += 1
-        e[1] += ms.value
+
+    # -- the per-kernel profile (src/gpu.rs:38-42, :198-222), kept by the library ------------
+    @property
+    def profile(self):
+        """None, or (while profiling) the table so far as {(phase, kernel): [launches, ms]}.
+        Assigning anything but None clears the table and starts profiling: every launch then
+        waits for its kernel and adds its device time; assigning None stops it."""
+        if not self._profiling:
+            return None
+        return {(p, k): [n, ms] for p, k, n, ms in self.profile_rows()}
+
+    @profile.setter
+    def profile(self, value) -> None:
+        self._profiling = value is not None
+        self._check(self._l.tb200_profile(self._h, 1 if self._profiling else 0))
+
+    @property
+    def phase(self) -> str:
+        return self._phase
+
+    @phase.setter
+    def phase(self, value: str) -> None:
+        if value != self._phase:
+            self._phase = value
+            self._check(self._l.tb200_phase(self._h, value.encode()))
+
+    def tune(self, k: K, args: Sequence[Arg]):
+        """Times the candidate tiles of projection kernel ``k`` on ``args`` and keeps the fastest
+        (``tb200_tune``; the reference's ``Engine::mm``, src/llm/engine.rs:233-270). Returns
+        ((MT, BN, splits), microseconds); whatever ``k`` writes is clobbered."""
+        raw = (C.c_uint64 * max(len(args), 1))(*[_bits(a) for a in args])
+        plan = (C.c_int32 * 3)()
+        us = C.c_float()
+        self._check(self._l.tb200_tune(self._h, k.id, raw, len(args), plan, C.byref(us)))
+        return tuple(plan), us.value
 
     def decode_attention_static(self, dims: Sequence[int], q: Buf, kc: Buf, vc: Buf, table: Buf, lens: Buf, o: Buf,
                                 scale: float) -> None:
@@ -203,8 +226,13 @@ class Gpu:
 
     def profile_rows(self):
         """The profile, largest first: (phase, kernel, launches, milliseconds)."""
-        rows = [(p, k, int(n), ms) for (p, k), (n, ms) in (self.profile or {}).items()]
-        rows.sort(key=lambda r: -r[3])
+        n = C.c_int()
+        self._check(self._l.tb200_profile_rows(self._h, C.byref(n)))
+        rows = []
+        for i in range(n.value):
+            ph, kn, cnt, ms = C.c_char_p(), C.c_char_p(), C.c_uint64(), C.c_double()
+            self._check(self._l.tb200_profile_row(self._h, i, C.byref(ph), C.byref(kn), C.byref(cnt), C.byref(ms)))
+            rows.append((ph.value.decode(), kn.value.decode(), int(cnt.value), float(ms.value)))
         return rows
 
     # -- graphs, sync, timing ----------------------------------------------------
