@@ -85,7 +85,15 @@ int tb200_host_free(tb200_ctx* ctx, void* ptr);
  * [base, base+N) as (value, index) in slot `rank`, zeros in the other slots, so
  * that tb200_allreduce gathers the slots) and argmax_merge (pairs f32[R,M,2],
  * out i32[M]: the first maximum over the ranks, the token src/llm/mod.rs:132-140
- * picks from the whole row). The
+ * picks from the whole row); and chunk_attention (Q[T,H,D], Kc[NP,P,G,D],
+ * Vc[NP,P,G,D], table[T,MP], meta i32[C,4], O[T,H,D], then the f32 scale):
+ * causal attention for the rows of prompts that are fed in pieces (the
+ * reference needs a prompt to fit one step, src/llm/sched.rs:76-81). Chunk c
+ * is rows [meta[c][0], meta[c][0] + meta[c][1]) of the step, the tokens at
+ * positions meta[c][2], meta[c][2] + 1, ... of their sequence, whose block
+ * table is row meta[c][0] of `table`; row r attends to cache positions 0 to
+ * its own, this step's keys included (kv_write runs first). Rows outside every
+ * chunk are not written. The
  * reference's `meta` and `warps` arguments have no equivalent: tile shapes are
  * chosen inside. */
 int tb200_kernel(tb200_ctx* ctx, const char* name, const int64_t* shapes, const int32_t* ranks, int n_arrays,

@@ -43,6 +43,7 @@ enum Kind : int {
   K_DECODE_ADVANCE, // next decode step's tok/pos/slot/lens from this step's picks, on the device
   K_ARGMAX_PARTIAL, // a rank's (maximum, index) over its slice of a vocabulary split across ranks
   K_ARGMAX_MERGE,   // first maximum over the ranks' parts
+  K_CHUNK_ATTENTION,  // causal attention of a prompt chunk's rows against the paged cache
   K_COUNT
 };
 

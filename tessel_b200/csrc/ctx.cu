@@ -86,6 +86,7 @@ static const KindInfo KINDS[] = {
     {"rope_kv", K_ROPE_KV, 10, 10},
     {"argmax_partial", K_ARGMAX_PARTIAL, 2, 4},
     {"argmax_merge", K_ARGMAX_MERGE, 2, 2},
+    {"chunk_attention", K_CHUNK_ATTENTION, 6, 7},
 };
 
 static std::string shape_text(const std::vector<int64_t>& s) {
@@ -322,7 +323,7 @@ int tb200_kernel(tb200_ctx* h, const char* name, const int64_t* shapes, const in
     r = make_gemm(c, op);
   else if (op.kind == K_DECODE_ATTENTION || op.kind == K_PAGED_ATTENTION)
     r = make_decode(c, op);
-  else if (op.kind == K_PREFILL_ATTENTION || op.kind == K_FLASH_ATTENTION)
+  else if (op.kind == K_PREFILL_ATTENTION || op.kind == K_FLASH_ATTENTION || op.kind == K_CHUNK_ATTENTION)
     r = make_prefill(c, op);
   else if (op.kind == K_TP_REDUCE_NORM)
     r = make_tp(c, op);
@@ -352,7 +353,7 @@ int tb200_launch(tb200_ctx* h, tb200_op id, const uint64_t* args, int n_args) {
     r = launch_gemm(c, op, args);
   else if (op.kind == K_DECODE_ATTENTION || op.kind == K_PAGED_ATTENTION)
     r = launch_decode(c, op, args);
-  else if (op.kind == K_PREFILL_ATTENTION || op.kind == K_FLASH_ATTENTION)
+  else if (op.kind == K_PREFILL_ATTENTION || op.kind == K_FLASH_ATTENTION || op.kind == K_CHUNK_ATTENTION)
     r = launch_prefill(c, op, args);
   else if (op.kind == K_TP_REDUCE_NORM)
     r = launch_tp(c, op, args);

@@ -59,6 +59,16 @@ class Decode:
     lens: Sequence[int]
 
 
+@dataclass
+class Mixed(Decode):
+    """A decode step that also carries the next pieces of prompts that do not fit one step:
+    ``chunks`` lists (row0, nrows, pos0) for each piece - rows [row0, row0 + nrows) of the step
+    are the tokens at positions pos0, pos0 + 1, ... of one sequence, whose pages are
+    ``tables[row0]``. Those rows are attended by ``chunk_attention`` (tensor cores, the paged
+    cache as K and V); their ``lens`` entries are ignored. Every other row is a decode row."""
+    chunks: Sequence[Sequence[int]] = ()
+
+
 def padded(n: int) -> int:
     """Rows a step is made for: at least 16, rounded up to a power of two (src/llm/engine.rs:94-98)."""
     n = max(n, 16)
@@ -182,6 +192,9 @@ class Engine:
         # Page-locked staging for a step's inputs and results.
         mp = lim.max_seq_pages
         self._stage = gpu.host_array((6 * t + t * mp,), np.int32)
+        self.meta = a(t * 4 * 4)  # chunk descriptors of a mixed step: (row0, nrows, pos0, -)
+        self._meta_stage = gpu.host_array((t, 4), np.int32)
+        self._chunks = 0
         self._picked_host = gpu.host_array((t,), np.int32)
         self._logits_host: Optional[np.ndarray] = None
         self._hist: Optional[Buf] = None
@@ -261,6 +274,17 @@ class Engine:
                 for b, row in enumerate(attn.tables):
                     tb[b, :len(row)] = row
             ln[:len(attn.lens)] = attn.lens
+            self._chunks = 0
+            if isinstance(attn, Mixed) and len(attn.chunks):
+                # Chunk rows are not decode rows: an empty length makes the decode kernel skip them.
+                nc = len(attn.chunks)
+                self._chunks = padded(nc) if nc > 16 else 1 << (nc - 1).bit_length()
+                mt = self._meta_stage[:self._chunks]
+                mt[:] = 0
+                for c, (row0, nrows, pos0) in enumerate(attn.chunks):
+                    mt[c, :3] = (row0, nrows, pos0)
+                    ln[row0:row0 + nrows] = 0
+                g.write_async(self.meta, 0, mt)
             g.write_async(self.table, 0, tb)
             g.write_async(self.lens, 0, ln)
         # Rows whose logits are wanted.
@@ -277,7 +301,7 @@ class Engine:
         g.phase = "prefill" if prefill else "decode"
         # Profiling times every launch on its own, so it runs without graphs.
         profiling = g._profiling if hasattr(g, "_profiling") else g.profile is not None
-        if (not prefill) and self.graphs and not profiling and bw == t:
+        if (not prefill) and self.graphs and not profiling and bw == t and not self._chunks:
             # A decode step of this size: replay its recorded launches, or run
             # them and record them for the next time.
             key = (t, greedy, self.fused)
@@ -389,6 +413,10 @@ class Engine:
         else:
             att = k("decode_attention", [[t, nh, hd], [lim.pages, lim.page, ng, hd], [lim.pages, lim.page, ng, hd],
                                          [t, mp], [t], [t, nh, hd]])
+        chunk_att = None
+        if not prefill and self._chunks:
+            cache = [lim.pages, lim.page, ng, hd]
+            chunk_att = k("chunk_attention", [[t, nh, hd], cache, cache, [t, mp], [self._chunks, 4], [t, nh, hd]])
         proj = "linear_f32" if tp else "linear_residual"
         acc = self.part if tp else self.x
         oproj = self._mm(proj, [[t, nh * hd], [dm, nh * hd], [t, dm]], [self.o, l0.wo, acc], t)
@@ -406,7 +434,7 @@ class Engine:
 
         g.launch(embed, [self.tok, self.embed, self.x])
         if self.tp_table is not None and self.fused:
-            self._launch_layers_fused(t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale)
+            self._launch_layers_fused(t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale, chunk_att)
             self._launch_head(t, bw, greedy, eps)
             return
         for l in self.layers:
@@ -417,13 +445,15 @@ class Engine:
                 g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
             else:
                 g.launch(att, [self.q, l.kc, l.vc, self.table, self.lens, self.o, scale])
+                if chunk_att is not None:
+                    g.launch(chunk_att, [self.q, l.kc, l.vc, self.table, self.meta, self.o, scale])
             project(oproj, self.o, l.wo)
             g.launch(norm, [self.x, l.n2, self.h, eps])
             g.launch(gu, [self.h, l.wg, l.wu, self.mlp])
             project(down, self.mlp, l.wd)
         self._launch_head(t, bw, greedy, eps)
 
-    def _launch_layers_fused(self, t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale) -> None:
+    def _launch_layers_fused(self, t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale, chunk_att=None) -> None:
         """The decoder layers under tensor parallelism with the fused cross-rank reduction: each
         projection pair ends in one ``tp_reduce_norm`` that sums the ranks' partials into the
         residual stream and writes the next layer input h on every rank."""
@@ -438,6 +468,8 @@ class Engine:
                 g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
             else:
                 g.launch(att, [self.q, l.kc, l.vc, self.table, self.lens, self.o, scale])
+                if chunk_att is not None:
+                    g.launch(chunk_att, [self.q, l.kc, l.vc, self.table, self.meta, self.o, scale])
             g.launch(oproj, [self.o, l.wo, self.part])
             g.launch(tpk, [self.tp_table, l.n2, self.x, eps, I32(0), I32(1), I32(self.nranks)])
             g.launch(gu, [self.h, l.wg, l.wu, self.mlp])

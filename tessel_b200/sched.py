@@ -13,10 +13,10 @@ one step (src/llm/sched.rs:76-81). With ``chunk > 0`` a longer prompt is
 admitted anyway and fed ``chunk`` tokens at a time as extra rows of the decode
 steps, each row attending, through the sequence's block table, to the keys
 cached so far (its own chunk's earlier tokens included: a step writes all its
-keys before its attention runs). These rows go through the paged decode
-attention, one row per token, so they cost far more per token than a prefill
-step does; the feature is for the occasional prompt that exceeds the step, not
-a replacement for prefill.
+keys before its attention runs). The step says which rows are such pieces
+(``engine.Mixed``), and the engine runs them through ``chunk_attention``: the
+prefill kernel's tensor-core pipeline with the paged cache as K and V, one CTA
+per 256 rows and head, instead of one decode query per token.
 """
 from __future__ import annotations
 
@@ -27,7 +27,7 @@ from typing import List, Sequence, Tuple
 
 import numpy as np
 
-from .engine import Decode, Engine, Packed, Prefill
+from .engine import Decode, Engine, Mixed, Packed, Prefill
 from .model import argmax
 
 
@@ -214,12 +214,14 @@ class Scheduler:
         want = list(range(len(run)))
         budget = e.lim.max_tokens - len(run)
         fed = []  # (sequence, tokens fed, row of its last prompt token or -1)
+        chunks = []  # (first row, rows, first position) of each piece, for the chunk attention
         for s in self.feeding:
             c = min(self.chunk, s.todo, budget)
             if c <= 0:
                 continue
             budget -= c
             pr = reqs[s.id].prompt
+            chunks.append((len(toks), c, s.len))
             for i in range(s.len, s.len + c):
                 toks.append(pr[i])
                 pos.append(i)
@@ -231,7 +233,7 @@ class Scheduler:
                 last = len(toks) - 1
                 want.append(last)
             fed.append((s, c, last))
-        picks = self._choose(Decode(tables, lens), toks, pos, slots, want)
+        picks = self._choose(Mixed(tables, lens, chunks), toks, pos, slots, want)
         if run:
             self.absorb(picks[:len(run)])
         st.prompt_tokens += sum(c for _, c, _ in fed)

@@ -135,6 +135,16 @@ class EmuGpu:
             A(3, h)[:] = oracle.flash_attention(A(0, h), A(1, h), A(2, h), sc(4))
         elif name in ("decode_attention", "paged_attention"):
             A(5, h)[:] = oracle.decode_attention(A(0, h), A(1, h), A(2, h), A(3, i), A(4, i), sc(6))
+        elif name == "chunk_attention":
+            # Row r of a chunk is a decode query with r + 1 more cached tokens than the chunk's start.
+            q, o, meta, table = A(0, h), A(5, h), A(4, i), A(3, i)
+            for row0, nrows, pos0, _ in meta:
+                if nrows <= 0:
+                    continue
+                rows = np.arange(row0, row0 + nrows)
+                tb = np.repeat(table[row0:row0 + 1], nrows, axis=0)
+                ln = (pos0 + 1 + np.arange(nrows)).astype(np.int32)
+                o[rows] = oracle.decode_attention(q[rows], A(1, h), A(2, h), tb, ln, sc(6))
         elif name == "residual_add":
             A(0, f)[:] = A(0, f) + A(1, f)
         elif name == "argmax_rows":

@@ -90,3 +90,49 @@ def test_config3_shape_sampled(gpu):
         want = oracle.flash_attention(q[hh:hh + 1], k[hh:hh + 1], v[hh:hh + 1], scale, blocks=(blk, blk + 1))
         rows = slice(blk * 64, blk * 64 + 64)
         assert rel_err(got[hh, rows], want[0, rows]) <= TOL
+
+
+@pytest.mark.parametrize("H,G,D,P,T,chunks", [
+    # (row0, nrows, pos0): rows of the step, tokens at positions pos0 ... of their sequence
+    (32, 8, 128, 16, 512, [(3, 300, 77), (303, 5, 0), (310, 128, 512)]),   # several 256-row CTAs; a start mid-page
+    (32, 4, 64, 16, 256, [(0, 256, 1000)]),                                 # TinyLlama grouping, a long cached prefix
+    (8, 2, 128, 16, 64, [(10, 48, 0), (58, 1, 333)]),                       # a first chunk (no cache yet); one row
+    (4, 2, 32, 8, 64, [(5, 40, 9)]),                                        # generic path: D = 32, page 8
+])
+def test_chunk_attention_against_decode_rows(gpu, H, G, D, P, T, chunks):
+    """Rows of prompts fed in pieces, attended through the paged cache: each row must equal the
+    decode attention of the same query with the cache cut off after its own position (which is how
+    the CPU engine computes it). Rows outside every chunk keep their contents."""
+    r = oracle.Rng(61)
+    g = np.random.default_rng(61)
+    need = [-(-(pos0 + n) // P) for _, n, pos0 in chunks]
+    MP, NP = max(need) + 1, sum(need) + 5
+    order = g.permutation(NP)
+    q = r.tensor(h, (T, H, D))
+    kc, vc = r.tensor(h, (NP, P, G, D)), r.tensor(h, (NP, P, G, D))
+    table = np.zeros((T, MP), i32)
+    meta = np.zeros((4, 4), i32)
+    at = 0
+    for c, ((row0, n, pos0), pages) in enumerate(zip(chunks, need)):
+        table[row0:row0 + n, :pages] = order[at:at + pages]
+        at += pages
+        meta[c, :3] = (row0, n, pos0)
+    scale = float(1.0 / np.sqrt(D))
+    sentinel = np.full((T, H, D), 7.0, h)
+    arrays = [q, kc, vc, table, meta, sentinel]
+    bufs = [gpu.tensor(a) for a in arrays]
+    kern = gpu.kernel("chunk_attention", [a.shape for a in arrays])
+    gpu.launch(kern, bufs + [F32(scale)])
+    gpu.sync()
+    got = gpu.fetch(bufs[5], h, q.shape)
+    for b in bufs:
+        gpu.free(b)
+    touched = np.zeros(T, bool)
+    for row0, n, pos0 in chunks:
+        rows = np.arange(row0, row0 + n)
+        touched[rows] = True
+        lens = (pos0 + 1 + np.arange(n)).astype(i32)
+        want = oracle.decode_attention(q[rows], kc, vc, table[rows], lens, scale)
+        assert not np.isnan(got[rows].astype(f)).any()
+        assert rel_err(got[rows], want) <= TOL, (row0, n, pos0)
+    assert np.array_equal(got[~touched].view(np.uint16), sentinel[~touched].view(np.uint16))
