@@ -182,23 +182,31 @@ int tb200_comm_init(tb200_ctx* ctx, int rank, int nranks, const void* id);
 int tb200_allreduce(tb200_ctx* ctx, uint64_t dptr, size_t count, int dtype);
 
 /* No counterpart in the reference: the cross-rank sum fused with the residual add
- * and the next RMSNorm, over peer memory (NVLink loads and stores) instead of an
- * NCCL call. Each rank allocates two partial-product buffers f32[T,dim], its
- * residual stream x f32[T,dim], h f16[T,dim], a staging buffer of T*dim*4 bytes
- * (its own h rows interleaved with a per-call counter, from which the peers
- * copy them), a flag area and an epoch area (tb200_tp_sizes; staging, flags and
- * epochs zero-filled, as tb200_alloc leaves them), exports them
- * with tb200_ipc_export (a 64-byte handle each), the host hands every rank the
- * others' handles, tb200_ipc_import maps them, and tb200_tp_table writes the
- * table (pointer arrays indexed by rank; a rank's own entries are its local
- * pointers) that the host then uploads to device memory. The kernel
- * "tp_reduce_norm" (arrays: table u8[bytes], W f16[dim], X f32[T,dim]; then
- * eps f32, which i32 = the partial buffer to sum, do_norm i32, nranks i32) adds
- * the ranks' partials in rank order to x and, if do_norm, normalises into h and
- * leaves h identical on every rank (x is then current only in the rows r with
- * r % nranks == rank); with do_norm = 0 it leaves x identical on every rank
- * instead. Every rank must launch it the same number of times with the same
- * shapes. */
+ * and the next RMSNorm, over peer memory (NVLink stores; every wait polls local
+ * memory) instead of an NCCL call. Row r of a step belongs to rank r % nranks.
+ * Each rank allocates two inboxes f32[nranks][ceil(T/nranks)][dim] (allocate
+ * (T + nranks) * dim * 4 bytes), its residual stream x f32[T,dim], h f16[T,dim],
+ * a landing area of T*dim*8 bytes (where the other owners' finished rows arrive
+ * as 8-byte units {payload, call counter}), a flag area and an epoch area
+ * (tb200_tp_sizes; landing area, flags and epochs zero-filled, as tb200_alloc
+ * leaves them), exports them with tb200_ipc_export (a 64-byte handle each), the
+ * host hands every rank the others' handles, tb200_ipc_import maps them, and
+ * tb200_tp_table writes the table (pointer arrays indexed by rank; a rank's own
+ * entries are its local pointers; `part0`/`part1` are the inboxes, `stage` the
+ * landing areas) that the host then uploads to device memory.
+ *
+ * The kernel "linear_scatter" (arrays: X f16[M,K], W f16[N,K], table u8[bytes];
+ * then which i32) is linear_f32 whose output row r is stored into inbox `which`
+ * of rank r % nranks, at [this rank][r / nranks] - the reduce-scatter, done by
+ * the projection itself. The kernel "tp_reduce_norm" (arrays: table u8[bytes],
+ * W f16[dim], X f32[T,dim]; then eps f32, which i32 = the inbox to sum, do_norm
+ * i32, nranks i32) runs behind it: it waits until every rank's projection is
+ * complete, adds the nranks partials of the rows this rank owns, in rank order,
+ * to x and, if do_norm, normalises them into h, sends the rows to every peer
+ * and collects the peers', which leaves h identical on every rank (x is then
+ * current only in the rows this rank owns); with do_norm = 0 it leaves x
+ * identical on every rank instead. Every rank must launch both the same number
+ * of times with the same shapes. */
 #define TB200_IPC_HANDLE_BYTES 64
 int tb200_ipc_export(tb200_ctx* ctx, uint64_t dptr, void* handle);
 int tb200_ipc_import(tb200_ctx* ctx, const void* handle, uint64_t* dptr);

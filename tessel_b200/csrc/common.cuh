@@ -44,6 +44,7 @@ enum Kind : int {
   K_ARGMAX_PARTIAL, // a rank's (maximum, index) over its slice of a vocabulary split across ranks
   K_ARGMAX_MERGE,   // first maximum over the ranks' parts
   K_CHUNK_ATTENTION,  // causal attention of a prompt chunk's rows against the paged cache
+  K_LINEAR_SCATTER,   // a tensor-parallel rank's partial product, each row stored into its owner rank's memory
   K_COUNT
 };
 
@@ -66,6 +67,8 @@ struct Op {
   size_t scratch_bytes = 0;
   // Kernel-specific tuning chosen when the op is made.
   int p0 = 0, p1 = 0, p2 = 0, p3 = 0;
+  // A scalar launch argument on its way into the kernel's parameters (linear_scatter: which inbox).
+  int aux = 0;
   std::vector<MapEntry> maps;
 
   // The cached maps for `key`, or null; `fresh` returns a slot to fill (the cache is emptied
@@ -130,6 +133,28 @@ int cuda_fail(Ctx* c, cudaError_t e, const char* what);
 // strides_bytes[i] is the stride of dims[i+1]. Returns 0 on success.
 int make_tensor_map(Ctx* c, CUtensorMap* out, CUtensorMapDataType dt, int rank, const void* base, const uint64_t* dims,
                     const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz);
+
+// ---- tensor-parallel exchange over peer memory (csrc/tp.cu, and the scatter epilogue of csrc/gemm.cu)
+constexpr int TP_MAX = 8;
+
+// Lives in device memory; written once by the host after the ranks exchanged IPC handles.
+// Pointer arrays are indexed by rank; a rank's own entries are its local pointers.
+//
+// Row r of a step belongs to rank r % n. part[w][o] is owner o's INBOX w: f32
+// [n sources][ceil(T / n) rows][dim], where source s's projection kernel stores its partial of
+// owner o's rows (linear_scatter). stage[o] is rank o's landing area for the other owners'
+// finished rows: 8-byte units {payload | epoch << 32}, [T][dim] units (payload: two halves of h
+// for the first dim / 2 units of a row, or one f32 of x for all dim units on the last call of a
+// step).
+struct TpTable {
+  float* part[2][TP_MAX];
+  float* x[TP_MAX];             // residual stream of every rank
+  __half* h[TP_MAX];            // normalised activations of every rank
+  unsigned long long* stage[TP_MAX];
+  unsigned int* flags[TP_MAX];  // [TP_SLOTS][TP_PHASES][TP_MAX senders]
+  unsigned int* epoch;          // [TP_SLOTS], local: launches this slot has taken part in
+  int rank, nranks;
+};
 
 // Launchers, one per kernel family. `a` holds the launch arguments as the C
 // ABI received them: device pointers, or scalar bits in the low 32 bits.

@@ -64,7 +64,19 @@ struct GemmParams {
   void* out;
   int M, N, K, splits;
   unsigned int* status;
+  // linear_scatter: row r goes to rank r % n's inbox `which`, at [this rank][r / n]; null otherwise.
+  const TpTable* scatter;
+  int which;
 };
+
+// Where output row `row` of an f32 product starts: in `out`, or (linear_scatter) in the inbox of
+// the rank that owns the row. The table is a few cache lines every thread of the grid reads.
+__device__ __forceinline__ float* f32_row(const GemmParams& p, int row) {
+  if (p.scatter == nullptr) return (float*)p.out + (size_t)row * p.N;
+  const int n = p.scatter->nranks, src = p.scatter->rank;
+  const int per = (p.M + n - 1) / n;
+  return p.scatter->part[p.which][row % n] + ((size_t)src * per + row / n) * p.N;
+}
 
 template <int MT, int BN, int EPI>
 struct GemmCfg {
@@ -116,7 +128,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
         if (j < ncols && col0 + j < p.N) y[j] = __float2half_rn(v[j]);
     }
   } else {
-    float* y = (float*)p.out + (size_t)row * p.N + col0;
+    float* y = (EPI == EPI_F32 ? f32_row(p, row) : (float*)p.out + (size_t)row * p.N) + col0;
     if (fullw) {
 #pragma unroll
       for (int j = 0; j < 32; j += 4) {
@@ -254,6 +266,9 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem
       }
     }
   }
+  // Rows stored into other GPUs' memory are acknowledged before this thread ends, so that the
+  // kernel's completion (which the next kernel announces to those GPUs) covers them.
+  if (EPI == EPI_F32 && p.scatter != nullptr && epi) __threadfence_system();
 }
 
 // B_MN: B is a [K, N] row-major array (N-major operand); else W [N, K] (K-major).
@@ -570,7 +585,7 @@ GemmShape gemm_shape(const Op& op) {
   g.M = (int)s[0][0];
   g.K = (int)s[0][1];
   g.N = op.kind == K_MATMUL ? (int)s[1][1] : (int)s[1][0];
-  return g;
+  return g;  // linear_scatter: X[M,K], W[N,K], table: the same two leading shapes
 }
 
 int epi_of(Kind k) {
@@ -641,6 +656,8 @@ int run(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, const voi
   p.K = g.K;
   p.splits = splits;
   p.status = c->status;
+  p.scatter = op.kind == K_LINEAR_SCATTER ? (const TpTable*)out : nullptr;
+  p.which = op.aux;
   const dim3 grid((g.M + MT * BM - 1) / (MT * BM), (g.N + BN - 1) / BN, splits);
   TB_CUDA(c, launch_k(c, gemm_kernel<MT, BN, EPI, B_MN>, grid, dim3(GEMM_THREADS), Cfg::SMEM, splits, ma, mb, mb2, p));
   return 0;
@@ -688,6 +705,8 @@ int run_pair(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, cons
   p.K = g.K;
   p.splits = splits;
   p.status = c->status;
+  p.scatter = op.kind == K_LINEAR_SCATTER ? (const TpTable*)out : nullptr;
+  p.which = op.aux;
   const dim3 grid(2 * ((g.M + 2 * BM - 1) / (2 * BM)), (g.N + BN - 1) / BN, splits);
   TB_CUDA(c, launch_kc(c, gemm_pair_kernel<BN, EPI>, grid, dim3(GEMM_THREADS), Cfg::SMEM, 2, splits, ma, mb, mb2, p));
   return 0;
@@ -878,10 +897,14 @@ std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
 int make_gemm(Ctx* c, Op& op) {
   const auto& s = op.shapes;
   auto bad = [&](const char* why) { return fail(c, op.name + ": " + why); };
-  for (auto& v : s)
-    if (v.size() != 2) return bad("every array is two-dimensional");
+  for (size_t i = 0; i < s.size(); ++i)
+    if (s[i].size() != 2 && !(op.kind == K_LINEAR_SCATTER && i == 2)) return bad("every array is two-dimensional");
   const GemmShape g = gemm_shape(op);
-  if (op.kind == K_MATMUL) {
+  if (op.kind == K_LINEAR_SCATTER) {
+    if (s[1][1] != g.K || s[2].size() != 1 || (size_t)s[2][0] < sizeof(TpTable))
+      return bad("shapes are X[M,K], W[N,K], table[bytes of tb200_tp_sizes]");
+    if (g.K <= 0 || g.K % 8 || g.N % 4) return bad("K must be a positive multiple of 8 and N a multiple of 4");
+  } else if (op.kind == K_MATMUL) {
     if (s[1][0] != g.K || s[2][0] != g.M || s[2][1] != g.N) return bad("shapes are A[M,K], B[K,N], C[M,N]");
   } else if (op.kind == K_GATE_UP) {
     if (s[1][1] != g.K || s[2] != s[1] || s[3][0] != g.M || s[3][1] != g.N)
@@ -920,6 +943,10 @@ namespace {
 // One launch of `op` with plan (mt, bn, splits) on the launch arguments `a`.
 int launch_plan(Ctx* c, Op& op, const uint64_t* a, int mt, int bn, int splits) {
   const GemmShape g = gemm_shape(op);
+  if (op.kind == K_LINEAR_SCATTER) {
+    op.aux = (int)(uint32_t)a[3];
+    if (op.aux < 0 || op.aux > 1) return fail(c, op.name + ": which is 0 or 1");
+  }
   const void* A = (const void*)a[0];
   const void* B = (const void*)a[1];
   const void* B2 = op.kind == K_GATE_UP ? (const void*)a[2] : nullptr;

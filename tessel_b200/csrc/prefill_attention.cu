@@ -60,7 +60,11 @@ __device__ __forceinline__ float exp2_sfu(float x) {
 // 1e-4, far inside the f16 rounding P gets next), and the integer part added to the exponent
 // field. The special-function unit computes 16 exponentials per clock per SM and the softmax
 // of a 128 x 64 score block needs as many of its cycles as the block's two MMAs need of the
-// tensor pipe, so a share of the exponentials is taken off it.
+// tensor pipe, so a share of the exponentials can be taken off it. Measured on the 8 x 32-head,
+// 4096-token, D = 128 case: 981 TFLOP/s with every exponential on the special-function unit, 930
+// with one in four here, 864 with one in two: the softmax warps are bound by instruction issue,
+// not by that unit, and the polynomial costs about ten instructions where ex2.approx costs one.
+// So the default keeps them all on the special-function unit; TB200_FA_POLY=4 selects the other.
 __device__ __forceinline__ float exp2_fma(float x) {
   x = fmaxf(x, -126.0f);  // masked scores (-inf) become 2^-126: zero once rounded to f16
   float r;
@@ -71,7 +75,7 @@ __device__ __forceinline__ float exp2_fma(float x) {
   p = fmaf(p, fr, 1.0f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
 }
-constexpr int FA_POLY_DEFAULT = 4;  // one pair of exponentials in this many goes to exp2_fma (0: none)
+constexpr int FA_POLY_DEFAULT = 0;  // one pair of exponentials in this many goes to exp2_fma (0: none)
 #ifdef TB200_TRACE
 __device__ unsigned long long* g_fa_trace = nullptr;  // [kind][block] timestamps (ns) of CTA (0, 0); development builds only
 #define FA_TRACE(kind, jb)                                                                \
@@ -660,22 +664,20 @@ int make_prefill(Ctx* c, Op& op) {
   if (f.D % 8 || f.D > 256) return bad("head_dim must be a multiple of 8, at most 256");
   op.p0 = (f.D == 64 || f.D == 128) && f.S > 0 ? 1 : 0;
   if (f.paged && (f.P != 16 || f.NP < 1 || f.MP < 1)) op.p0 = 0;  // the page boxes are 16 tokens tall
-  // TB200_FA_POLY = 0, 2 or 4 (tuning): the share of exponentials computed off the special-function unit.
+  // TB200_FA_POLY = 0 or 4 (tuning): the share of exponentials computed off the special-function unit.
   op.p1 = FA_POLY_DEFAULT;
   if (const char* e = getenv("TB200_FA_POLY")) {
     op.p1 = atoi(e);
-    if (op.p1 != 0 && op.p1 != 2 && op.p1 != 4) return bad("TB200_FA_POLY is 0, 2 or 4");
+    if (op.p1 != 0 && op.p1 != 4) return bad("TB200_FA_POLY is 0 or 4");
   }
   if (op.p0) {
 #define TB_FA_ATTR(D_, P_) \
   TB_CUDA(c, cudaFuncSetAttribute(fa_kernel<D_, P_>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<D_>::TOTAL))
     if (f.D == 128) {
       if (op.p1 == 0) TB_FA_ATTR(128, 0);
-      else if (op.p1 == 2) TB_FA_ATTR(128, 2);
       else TB_FA_ATTR(128, 4);
     } else {
       if (op.p1 == 0) TB_FA_ATTR(64, 0);
-      else if (op.p1 == 2) TB_FA_ATTR(64, 2);
       else TB_FA_ATTR(64, 4);
     }
 #undef TB_FA_ATTR
@@ -696,13 +698,9 @@ int launch_prefill(Ctx* c, Op& op, const uint64_t* a) {
     int r;
     if (op.p0) {
       if (f.D == 128)
-        r = op.p1 == 0   ? run_fa<128, 0>(c, op, f, Q, K, V, nullptr, O, scale, table, meta)
-            : op.p1 == 2 ? run_fa<128, 2>(c, op, f, Q, K, V, nullptr, O, scale, table, meta)
-                         : run_fa<128, 4>(c, op, f, Q, K, V, nullptr, O, scale, table, meta);
+        r = op.p1 == 0 ? run_fa<128, 0>(c, op, f, Q, K, V, nullptr, O, scale, table, meta) : run_fa<128, 4>(c, op, f, Q, K, V, nullptr, O, scale, table, meta);
       else
-        r = op.p1 == 0   ? run_fa<64, 0>(c, op, f, Q, K, V, nullptr, O, scale, table, meta)
-            : op.p1 == 2 ? run_fa<64, 2>(c, op, f, Q, K, V, nullptr, O, scale, table, meta)
-                         : run_fa<64, 4>(c, op, f, Q, K, V, nullptr, O, scale, table, meta);
+        r = op.p1 == 0 ? run_fa<64, 0>(c, op, f, Q, K, V, nullptr, O, scale, table, meta) : run_fa<64, 4>(c, op, f, Q, K, V, nullptr, O, scale, table, meta);
     } else {
       const long long warps = (long long)f.S * f.H;  // at most T rows per chunk
       TB_CUDA(c, launch_k(c, chunk_generic_kernel, dim3((unsigned)((warps + 3) / 4), f.C), dim3(128), 0, 1,
@@ -722,13 +720,9 @@ int launch_prefill(Ctx* c, Op& op, const uint64_t* a) {
   int r;
   if (op.p0) {
     if (f.D == 128)
-      r = op.p1 == 0   ? run_fa<128, 0>(c, op, f, Q, K, V, starts, O, scale)
-          : op.p1 == 2 ? run_fa<128, 2>(c, op, f, Q, K, V, starts, O, scale)
-                       : run_fa<128, 4>(c, op, f, Q, K, V, starts, O, scale);
+      r = op.p1 == 0 ? run_fa<128, 0>(c, op, f, Q, K, V, starts, O, scale) : run_fa<128, 4>(c, op, f, Q, K, V, starts, O, scale);
     else
-      r = op.p1 == 0   ? run_fa<64, 0>(c, op, f, Q, K, V, starts, O, scale)
-          : op.p1 == 2 ? run_fa<64, 2>(c, op, f, Q, K, V, starts, O, scale)
-                       : run_fa<64, 4>(c, op, f, Q, K, V, starts, O, scale);
+      r = op.p1 == 0 ? run_fa<64, 0>(c, op, f, Q, K, V, starts, O, scale) : run_fa<64, 4>(c, op, f, Q, K, V, starts, O, scale);
   } else {
     const long long warps = (long long)f.S * f.H;
     TB_CUDA(c, launch_k(c, fa_generic_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), 0, 1, (const __half*)Q, (const __half*)K,

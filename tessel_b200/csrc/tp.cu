@@ -3,78 +3,62 @@
 // Under tensor parallelism o_proj and down_proj leave, on every rank, an f32 partial product
 // part[T, dim] whose sum over ranks must be added to the residual stream x and then normalised
 // into h for the next projection. The plain path does that with four launches: linear_f32, an
-// NCCL allreduce, residual_add, rmsnorm. `tp_reduce_norm` does the last three in ONE kernel over
-// peer memory (buffers of the other ranks mapped through CUDA IPC and reached over NVLink with
-// ordinary loads; no multicast, no TMA, and no stores into a peer's memory other than flags):
+// NCCL allreduce, residual_add, rmsnorm. Here the data only ever travels one way over NVLink, in
+// stores (buffers of the other ranks are mapped through CUDA IPC; no multicast, no TMA on peer
+// memory), and every wait polls LOCAL memory:
 //
-//   1. every CTA tells the same-numbered CTA of every peer that this rank's partial is
-//      complete (the kernel runs behind the rank's GEMM on the same stream) and waits for theirs;
-//   2. row r of the step belongs to rank r % n: its owner loads that row of all n partials
-//      (peers' over NVLink), adds them in rank order to its x row, normalises, and stores the
-//      new x row and h row in ITS OWN memory (the reduce-scatter);
-//   3. every CTA copies the other owners' h rows from their memory into its own h (the
-//      all-gather, pulled: a pushed copy would need a system-wide fence that waits for every
-//      remote store to be acknowledged, measured at 6-9 us per call). The owner publishes a row
-//      in a staging buffer whose every 8 bytes hold two halves and the call's epoch, written
-//      and read as ONE 64-bit value each (a single-copy-atomic access: payload and tag cannot be
-//      seen torn), so a reader knows from the data itself whether it is current and polls the
-//      row directly: no "rows are ready" flag, no release fence.
+//   0. (in the projection itself, `linear_scatter`, csrc/gemm.cu) row r of the step belongs to
+//      rank r % n: every rank's projection stores its partial of that row straight into the
+//      owner's inbox, [source rank][r / n][dim] f32 - the reduce-scatter, overlapped with the
+//      projection's own tail;
+//   1. `tp_reduce_norm`: every CTA tells the same-numbered CTA of every peer that this rank's
+//      projection is complete (the kernel runs behind it on the same stream) and waits for theirs;
+//   2. the owner adds the n partials of its rows in rank order (its inbox is local memory) to its
+//      x rows, normalises, keeps the new x and h rows, and stores each h row into every peer's
+//      landing area as 8-byte units {two halves | the call's epoch << 32}: one 64-bit store
+//      each, single-copy atomic, so a unit is either old or complete;
+//   3. every CTA polls its own landing area for the other owners' rows until every unit carries
+//      this call's epoch, and copies the payloads into h (the all-gather). The data says itself
+//      when it has arrived: no "rows are ready" flag, no fence over outstanding remote stores
+//      (a pushed copy closed by a barrier was measured: its system-wide fence alone took 6-9 us).
 //
 // Between layers only h is gathered: the residual stream stays distributed (a rank's x is
 // current in the rows it owns), because nothing but this kernel reads it. The last call of a
-// step (do_norm = 0) gathers x instead, for the final norm and the LM head, behind a second
-// flag exchange ("my rows are ready", a release), and closes with a third ("I have finished
-// reading"): the peers copy the rows straight out of this rank's x, and the very next kernel of
-// a step (embed) overwrites x, so the call may not return before every peer is done with it.
+// step (do_norm = 0) gathers x instead, for the final norm and the LM head, the same way with one
+// f32 per unit.
 //
 // Sums are taken in rank order by one owner, so x and h are bit-identical on all ranks, which
-// keeps the ranks' greedy tokens in lockstep. Flag waits are bounded: on time-out the kernel
-// raises the context's status word and returns.
+// keeps the ranks' greedy tokens in lockstep. Waits are bounded: on time-out the kernel raises
+// the context's status word and returns.
 //
-// Why the partial and staging buffers can be reused without a closing barrier: a rank
-// overwrites its partial, or its staged rows, only after step 1 of a later call, i.e. after
-// every peer has begun that call and therefore finished reading in this one. (x is the
-// exception, hence the third exchange above.)
+// Why nothing needs a closing barrier: a rank stores into a peer's inbox or landing area only
+// after step 1 of a later call (the projection that fills inbox w runs behind the call that
+// used inbox 1 - w), i.e. after that peer has begun the later call and therefore finished
+// reading in this one. Nobody reads another rank's x, h or inbox.
 //
 // Step 1's signal is a relaxed store: what it announces was written by the PREVIOUS kernel of
-// the stream, and a kernel's global writes are complete and visible system-wide when its
-// successor starts (the stream order; with programmatic dependent launch, after
-// griddepcontrol.wait). No fence of this kernel could add anything to that.
+// the stream, whose threads fenced their remote stores before they ended, and a kernel's writes
+// are complete when its successor starts (the stream order; with programmatic dependent launch,
+// after griddepcontrol.wait).
 #include "common.cuh"
 
 namespace tb {
 
 namespace {
 
-constexpr int TP_MAX = 8;
 constexpr int TP_SLOTS = 4096;  // CTAs a launch may have (rows of the largest step / ranks)
-constexpr int TP_THREADS = 1024;
-constexpr int TP_PHASES = 4;  // flag words per (slot, sender): partial ready, x rows ready, done reading, spare
+constexpr int TP_THREADS = 512;  // 128 registers a thread: the gather keeps eight owners' units in flight
+constexpr int TP_PHASES = 4;  // flag words per (slot, sender): projection complete; three spare
 
-// Lives in device memory; written once by the host after the ranks exchanged IPC handles.
-struct TpTable {
-  float* part[2][TP_MAX];   // the two partial-product buffers of every rank
-  float* x[TP_MAX];         // residual stream of every rank
-  __half* h[TP_MAX];        // normalised activations of every rank
-  uint4* stage[TP_MAX];     // [T, dim/4]: a rank's own h rows as two 64-bit units {2 halves | epoch << 32}
-  unsigned int* flags[TP_MAX];  // [TP_SLOTS][TP_PHASES][TP_MAX senders]
-  unsigned int* epoch;      // [TP_SLOTS], local: launches this slot has taken part in
-  int rank, nranks;
-};
-
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-
 __device__ __forceinline__ void st_relaxed_sys(unsigned int* p, unsigned int v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Loads that always go to the owner's L2 (never a stale line of this SM's L1).
+// Loads that always go to L2, where stores from other GPUs land (never a stale line of this SM's L1).
 __device__ __forceinline__ float4 ld_sys_f4(const float* p) {
   float4 v;
   asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
@@ -88,29 +72,24 @@ __device__ __forceinline__ float4 ld_sys_f4(const float* p) {
 struct Unit2 {
   unsigned long long a, b;
 };
-__device__ __forceinline__ Unit2 ld_sys_units(const uint4* p) {
+__device__ __forceinline__ Unit2 ld_sys_units(const unsigned long long* p) {
   Unit2 v;
   asm volatile("ld.relaxed.sys.global.v2.b64 {%0,%1}, [%2];" : "=l"(v.a), "=l"(v.b) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_sys_units(uint4* p, unsigned int lo0, unsigned int lo1, unsigned int tag) {
+__device__ __forceinline__ void st_sys_units(unsigned long long* p, unsigned int lo0, unsigned int lo1,
+                                             unsigned int tag) {
   const unsigned long long a = (unsigned long long)lo0 | ((unsigned long long)tag << 32);
   const unsigned long long b = (unsigned long long)lo1 | ((unsigned long long)tag << 32);
   asm volatile("st.relaxed.sys.global.v2.b64 [%0], {%1,%2};" ::"l"(p), "l"(a), "l"(b) : "memory");
 }
 
 // Thread `tid` < nranks signals peer `tid` and waits for peer `tid`'s signal of this epoch.
-// `release`: the signal publishes stores of this CTA (made before the preceding __syncthreads);
-// without it the signal only says that the previous kernel of this stream has completed.
 __device__ __forceinline__ void exchange_flags(const TpTable& tb_, int slot, int phase, unsigned int epoch,
-                                               bool release, unsigned int* status, unsigned int code) {
+                                               unsigned int* status, unsigned int code) {
   const int tid = threadIdx.x;
   if (tid < tb_.nranks && tid != tb_.rank) {
-    unsigned int* theirs = tb_.flags[tid] + ((size_t)slot * TP_PHASES + phase) * TP_MAX + tb_.rank;
-    if (release)
-      st_release_sys(theirs, epoch);
-    else
-      st_relaxed_sys(theirs, epoch);
+    st_relaxed_sys(tb_.flags[tid] + ((size_t)slot * TP_PHASES + phase) * TP_MAX + tb_.rank, epoch);
     const unsigned int* mine = tb_.flags[tb_.rank] + ((size_t)slot * TP_PHASES + phase) * TP_MAX + tid;
     const unsigned long long t0 = globaltimer();
     unsigned int spins = 0;
@@ -140,7 +119,46 @@ __device__ __forceinline__ void exchange_flags(const TpTable& tb_, int slot, int
   } while (0)
 #endif
 
-template <int PER>  // float4 chunks per thread: dim <= PER * 4096
+__device__ __forceinline__ bool current(const Unit2& u, unsigned int epoch) {
+  return (unsigned int)(u.a >> 32) == epoch && (unsigned int)(u.b >> 32) == epoch;
+}
+
+// Reads, for every other owner r, the two units at `land + (base + r) * row_units + off` of this
+// rank's landing area, polling until they carry `epoch` (all loads are issued before any is
+// tested: the rows mostly arrive together). Returns the owners whose units never came.
+__device__ __forceinline__ unsigned int gather_units(const unsigned long long* land, size_t row_units, size_t off,
+                                                     int base, int T, int n, int rank, unsigned int epoch,
+                                                     Unit2 (&v)[TP_MAX], unsigned int* status) {
+  unsigned int pending = 0;
+#pragma unroll
+  for (int r = 0; r < TP_MAX; ++r)
+    if (r < n && r != rank && base + r < T) {
+      v[r] = ld_sys_units(land + (size_t)(base + r) * row_units + off);
+      if (!current(v[r], epoch)) pending |= 1u << r;
+    }
+  if (pending) {
+    const unsigned long long t0 = globaltimer();
+    unsigned int spins = 0;
+    while (pending) {
+#pragma unroll
+      for (int r = 0; r < TP_MAX; ++r)
+        if (pending & (1u << r)) {
+          v[r] = ld_sys_units(land + (size_t)(base + r) * row_units + off);
+          if (current(v[r], epoch)) pending &= ~(1u << r);
+        }
+      if ((++spins & 63u) == 0) {
+        if (*(volatile unsigned int*)status != 0) break;
+        if (globaltimer() - t0 > WAIT_LIMIT_NS / 2) {
+          atomicCAS(status, 0u, 402u);
+          break;
+        }
+      }
+    }
+  }
+  return pending;
+}
+
+template <int PER>  // float4 chunks per thread: dim <= PER * 4 * TP_THREADS
 __global__ void __launch_bounds__(TP_THREADS, 1)
     tp_reduce_norm_kernel(const TpTable* __restrict__ table, const __half* __restrict__ W, float eps, int T, int dim,
                           int which, int do_norm, unsigned int* status) {
@@ -158,26 +176,27 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
   __syncthreads();
   const unsigned int epoch = s_epoch;
   const int n = tb_.nranks, rank = tb_.rank;
+  const int per = (T + n - 1) / n;  // rows of a source's share of an inbox
   TP_TRACE(0);
-  // 1. The partials were written by the previous kernel of each rank's stream, which has
-  // completed (and flushed to that rank's L2, where peers read them) before this one signals.
-  exchange_flags(tb_, blockIdx.x, 0, epoch, false, status, 401);
+  // 1. Every rank's projection (and with it its stores into the owners' inboxes) is complete.
+  exchange_flags(tb_, blockIdx.x, 0, epoch, status, 401);
   __syncthreads();
   TP_TRACE(1);
 
-  // 2. This rank's rows.
+  // 2. This rank's rows: sum the inbox in rank order, add to x, normalise, send to every peer.
+  const float* inbox = tb_.part[which][rank];
   for (int row = blockIdx.x * n + rank; row < T; row += gridDim.x * n) {
+    const int slot = row / n;
     float4 acc[PER];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < PER; ++i) {
       const int c = (threadIdx.x + i * TP_THREADS) * 4;
       if (c < dim) {
-        const size_t o = (size_t)row * dim + c;
         float4 part[TP_MAX];
 #pragma unroll
         for (int r = 0; r < TP_MAX; ++r)
-          if (r < n) part[r] = ld_sys_f4(tb_.part[which][r] + o);
+          if (r < n) part[r] = ld_sys_f4(inbox + ((size_t)r * per + slot) * dim + c);
         float4 s = part[0];
 #pragma unroll
         for (int r = 1; r < TP_MAX; ++r)
@@ -187,6 +206,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
             s.z = __fadd_rn(s.z, part[r].z);
             s.w = __fadd_rn(s.w, part[r].w);
           }
+        const size_t o = (size_t)row * dim + c;
         float4 x = *reinterpret_cast<const float4*>(tb_.x[rank] + o);
         x.x = __fadd_rn(x.x, s.x);
         x.y = __fadd_rn(x.y, s.y);
@@ -198,6 +218,16 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
         ss += __fmul_rn(x.y, x.y);
         ss += __fmul_rn(x.z, x.z);
         ss += __fmul_rn(x.w, x.w);
+        if (!do_norm) {
+          // The last call of a step: every rank gets the finished x row, one f32 per unit.
+#pragma unroll
+          for (int r = 0; r < TP_MAX; ++r)
+            if (r < n && r != rank) {
+              unsigned long long* dst = tb_.stage[r] + o;
+              st_sys_units(dst, __float_as_uint(x.x), __float_as_uint(x.y), epoch);
+              st_sys_units(dst + 2, __float_as_uint(x.z), __float_as_uint(x.w), epoch);
+            }
+        }
       }
     }
     if (do_norm) {
@@ -206,7 +236,7 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
       __syncthreads();
-      float tot = red[threadIdx.x & 31];
+      float tot = (threadIdx.x & 31) < TP_THREADS / 32 ? red[threadIdx.x & 31] : 0.f;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
       __syncthreads();
@@ -224,104 +254,59 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
           y.y = pack_h2(__fmul_rn(__fmul_rn(acc[i].z, rs), __low2float(w23)),
                         __fmul_rn(__fmul_rn(acc[i].w, rs), __high2float(w23)));
           *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)row * dim + c) = y;
-          st_sys_units(tb_.stage[rank] + (((size_t)row * dim + c) >> 2), y.x, y.y, epoch);
+          // Units c/2 and c/2 + 1 of the row in every peer's landing area.
+#pragma unroll
+          for (int r = 0; r < TP_MAX; ++r)
+            if (r < n && r != rank) st_sys_units(tb_.stage[r] + (size_t)row * dim + (c >> 1), y.x, y.y, epoch);
         }
       }
     }
   }
   TP_TRACE(2);
-  if (do_norm) {
-    // 3a. The other owners' h rows, polled until both halves of a 16-byte unit carry this epoch.
-    for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
+  // 3. The other owners' rows, from this rank's own landing area.
+  const unsigned long long* land = tb_.stage[rank];
+  for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
 #pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        const int c = (threadIdx.x + i * TP_THREADS) * 4;
-        if (c < dim) {
-          Unit2 v[TP_MAX];
-          unsigned int pending = 0;
-          auto current = [&](const Unit2& u) {
-            return (unsigned int)(u.a >> 32) == epoch && (unsigned int)(u.b >> 32) == epoch;
-          };
+    for (int i = 0; i < PER; ++i) {
+      const int c = (threadIdx.x + i * TP_THREADS) * 4;
+      if (c >= dim) continue;
+      Unit2 v[TP_MAX];
+      if (do_norm) {
+        gather_units(land, (size_t)dim, (size_t)(c >> 1), base, T, n, rank, epoch, v, status);
 #pragma unroll
-          for (int r = 0; r < TP_MAX; ++r)
-            if (r < n && r != rank && base + r < T) {
-              v[r] = ld_sys_units(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
-              if (!current(v[r])) pending |= 1u << r;
-            }
-          if (pending) {
-            const unsigned long long t0 = globaltimer();
-            unsigned int spins = 0;
-            while (pending) {
+        for (int r = 0; r < TP_MAX; ++r)
+          if (r < n && r != rank && base + r < T)
+            *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)(base + r) * dim + c) =
+                make_uint2((unsigned int)v[r].a, (unsigned int)v[r].b);
+      } else {
 #pragma unroll
-              for (int r = 0; r < TP_MAX; ++r)
-                if (pending & (1u << r)) {
-                  v[r] = ld_sys_units(tb_.stage[r] + (((size_t)(base + r) * dim + c) >> 2));
-                  if (current(v[r])) pending &= ~(1u << r);
-                }
-              if ((++spins & 63u) == 0) {
-                if (*(volatile unsigned int*)status != 0) break;
-                if (globaltimer() - t0 > WAIT_LIMIT_NS / 2) {
-                  atomicCAS(status, 0u, 402u);
-                  break;
-                }
-              }
-            }
-          }
+        for (int half = 0; half < 2; ++half) {
+          gather_units(land, (size_t)dim, (size_t)(c + 2 * half), base, T, n, rank, epoch, v, status);
 #pragma unroll
           for (int r = 0; r < TP_MAX; ++r)
             if (r < n && r != rank && base + r < T)
-              *reinterpret_cast<uint2*>(tb_.h[rank] + (size_t)(base + r) * dim + c) =
-                  make_uint2((unsigned int)v[r].a, (unsigned int)v[r].b);
+              *reinterpret_cast<float2*>(tb_.x[rank] + (size_t)(base + r) * dim + c + 2 * half) =
+                  make_float2(__uint_as_float((unsigned int)v[r].a), __uint_as_float((unsigned int)v[r].b));
         }
       }
     }
-    TP_TRACE(3);
-  } else {
-    // 3b. Publish this CTA's x rows (the release orders the CTA's stores, made before the
-    // barrier, ahead of the flag), wait for the other owners, and copy their rows.
-    __syncthreads();
-    exchange_flags(tb_, blockIdx.x, 1, epoch, true, status, 403);
-    __syncthreads();
-    TP_TRACE(3);
-    for (int base = blockIdx.x * n; base < T; base += gridDim.x * n) {
-#pragma unroll
-      for (int i = 0; i < PER; ++i) {
-        const int c = (threadIdx.x + i * TP_THREADS) * 4;
-        if (c < dim) {
-          float4 v[TP_MAX];
-#pragma unroll
-          for (int r = 0; r < TP_MAX; ++r)
-            if (r < n && r != rank && base + r < T) v[r] = ld_sys_f4(tb_.x[r] + (size_t)(base + r) * dim + c);
-#pragma unroll
-          for (int r = 0; r < TP_MAX; ++r)
-            if (r < n && r != rank && base + r < T)
-              *reinterpret_cast<float4*>(tb_.x[rank] + (size_t)(base + r) * dim + c) = v[r];
-        }
-      }
-    }
-    // 3c. The peers read this rank's rows out of x itself, which the next step's first kernel
-    // overwrites: stay until each of them says it has finished (its loads have returned: the
-    // values were stored before its barrier).
-    __syncthreads();
-    exchange_flags(tb_, blockIdx.x, 2, epoch, false, status, 404);
-    __syncthreads();
   }
-  TP_TRACE(4);
+  TP_TRACE(3);
   if (threadIdx.x == 0) tb_.epoch[blockIdx.x] = epoch;
 }
 
 }  // namespace
 
 // Shapes: table u8[bytes], W f16[dim], X f32[T, dim]. Arguments: table, W, X (this rank's own
-// residual stream; it must be the buffer the table names), eps, which (0/1: the partial buffer
-// this projection wrote), do_norm, nranks (the table's).
+// residual stream; it must be the buffer the table names), eps, which (0/1: the inbox the
+// projection filled), do_norm, nranks (the table's).
 int make_tp(Ctx* c, Op& op) {
   const auto& s = op.shapes;
   if (s[0].size() != 1 || s[1].size() != 1 || s[2].size() != 2 || s[1][0] != s[2][1])
     return fail(c, op.name + ": shapes are table[bytes], W[dim], X[T, dim]");
   if ((size_t)s[0][0] < sizeof(TpTable)) return fail(c, op.name + ": the table is too small");
   const int64_t dim = s[2][1];
-  if (dim % 4 || dim > 2 * 4 * TP_THREADS) return fail(c, op.name + ": dim must be a multiple of 4, at most 8192");
+  if (dim % 4 || dim > 4 * 4 * TP_THREADS) return fail(c, op.name + ": dim must be a multiple of 4, at most 8192");
   return 0;
 }
 
@@ -339,11 +324,11 @@ int launch_tp(Ctx* c, Op& op, const uint64_t* a) {
   int grid = (T + nranks - 1) / nranks;
   if (grid > c->sm_count) grid = c->sm_count;
   if (grid > TP_SLOTS) grid = TP_SLOTS;
-  if (dim <= 4 * TP_THREADS)
-    TB_CUDA(c, launch_k(c, tp_reduce_norm_kernel<1>, dim3(grid), dim3(TP_THREADS), 0, 1, (const TpTable*)a[0], (const __half*)a[1], eps, T,
+  if (dim <= 2 * 4 * TP_THREADS)
+    TB_CUDA(c, launch_k(c, tp_reduce_norm_kernel<2>, dim3(grid), dim3(TP_THREADS), 0, 1, (const TpTable*)a[0], (const __half*)a[1], eps, T,
                                                                  dim, which, do_norm, c->status));
   else
-    TB_CUDA(c, launch_k(c, tp_reduce_norm_kernel<2>, dim3(grid), dim3(TP_THREADS), 0, 1, (const TpTable*)a[0], (const __half*)a[1], eps, T,
+    TB_CUDA(c, launch_k(c, tp_reduce_norm_kernel<4>, dim3(grid), dim3(TP_THREADS), 0, 1, (const TpTable*)a[0], (const __half*)a[1], eps, T,
                                                                  dim, which, do_norm, c->status));
   TB_CUDA(c, cudaGetLastError());
   c->launches += 1;
@@ -365,7 +350,7 @@ int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint6
     t.part[1][r] = (float*)part1[r];
     t.x[r] = (float*)x[r];
     t.h[r] = (__half*)h[r];
-    t.stage[r] = (uint4*)stage[r];
+    t.stage[r] = (unsigned long long*)stage[r];
     t.flags[r] = (unsigned int*)flags[r];
   }
   t.epoch = (unsigned int*)epoch;

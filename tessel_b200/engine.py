@@ -16,8 +16,9 @@ integers come back instead of ``len(want) * vocab`` floats, and
 model can be tensor-parallel (``rank``/``nranks``): attention and KV heads and
 the MLP columns are sharded, o_proj and down_proj produce f32 partials that
 are summed across ranks before they are added to the residual stream, by one
-NCCL allreduce each or, given ``exchange``, by one kernel over peer memory that
-also does the residual add and the next RMSNorm; greedy steps then split the
+NCCL allreduce each or, given ``exchange``, over peer memory: the projection
+stores every row into its owner rank's memory and one more kernel sums, adds
+the residual, normalises and hands the rows round; greedy steps then split the
 LM head's rows across the ranks too.
 """
 from __future__ import annotations
@@ -184,7 +185,9 @@ class Engine:
         self.mlp = a(t * cfg.ffn * 2)
         self.last = a(t * cfg.dim * 2)
         self.logits = a(t * cfg.vocab * 4)
-        self.part = a(t * cfg.dim * 4) if nranks > 1 else None  # a rank's partial o_proj / down_proj
+        # A rank's partial o_proj / down_proj [t, dim] f32; with the peer-memory exchange, this
+        # rank's inbox: [sources][ceil(t / nranks)][dim], the peers' partials of the rows it owns.
+        self.part = a((t + nranks) * cfg.dim * 4) if nranks > 1 else None
         self.tok, self.pos, self.slot, self.idx = a(t * 4), a(t * 4), a(t * 4), a(t * 4)
         self.table = a(t * lim.max_seq_pages * 4)
         self.lens, self.starts = a(t * 4), a(t * 4)
@@ -215,8 +218,9 @@ class Engine:
         self.fused = nranks > 1 and exchange is not None
         if nranks > 1 and exchange is not None:
             _, fb, eb = gpu.tp_sizes()
-            self.part2 = a(t * cfg.dim * 4)
-            self.tp_stage = a(t * cfg.dim * 4)  # this rank's h rows, tagged with the call's epoch, for the peers
+            self.part2 = a((t + nranks) * cfg.dim * 4)
+            # Where the other owners' finished rows land: 8-byte units {payload | call counter}.
+            self.tp_stage = a(t * cfg.dim * 8)
             self.tp_flags, self.tp_epoch = a(fb), a(eb)
             mine = [self.part, self.part2, self.x, self.h, self.tp_stage, self.tp_flags]
             everyone = exchange([gpu.ipc_export(b) for b in mine])
@@ -417,11 +421,18 @@ class Engine:
         if not prefill and self._chunks:
             cache = [lim.pages, lim.page, ng, hd]
             chunk_att = k("chunk_attention", [[t, nh, hd], cache, cache, [t, mp], [self._chunks, 4], [t, nh, hd]])
-        proj = "linear_f32" if tp else "linear_residual"
-        acc = self.part if tp else self.x
-        oproj = self._mm(proj, [[t, nh * hd], [dm, nh * hd], [t, dm]], [self.o, l0.wo, acc], t)
         gu = self._mm("gate_up", [[t, dm], [f, dm], [f, dm], [t, f]], [self.h, l0.wg, l0.wu, self.mlp], t)
-        down = self._mm(proj, [[t, f], [dm, f], [t, dm]], [self.mlp, l0.wd, acc], t)
+        if self.tp_table is not None and self.fused:
+            # Each row of a partial product goes straight into its owner rank's inbox.
+            from .gpu import I32
+            tb = self.tp_table
+            oproj = self._mm("linear_scatter", [[t, nh * hd], [dm, nh * hd], [tb.bytes]], [self.o, l0.wo, tb, I32(0)], t)
+            down = self._mm("linear_scatter", [[t, f], [dm, f], [tb.bytes]], [self.mlp, l0.wd, tb, I32(1)], t)
+        else:
+            proj = "linear_f32" if tp else "linear_residual"
+            acc = self.part if tp else self.x
+            oproj = self._mm(proj, [[t, nh * hd], [dm, nh * hd], [t, dm]], [self.o, l0.wo, acc], t)
+            down = self._mm(proj, [[t, f], [dm, f], [t, dm]], [self.mlp, l0.wd, acc], t)
         radd = k("residual_add", [[t, dm], [t, dm]]) if tp else None
 
         def project(kern: K, x: Buf, wt: Buf) -> None:
@@ -454,9 +465,10 @@ class Engine:
         self._launch_head(t, bw, greedy, eps)
 
     def _launch_layers_fused(self, t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale, chunk_att=None) -> None:
-        """The decoder layers under tensor parallelism with the fused cross-rank reduction: each
-        projection pair ends in one ``tp_reduce_norm`` that sums the ranks' partials into the
-        residual stream and writes the next layer input h on every rank."""
+        """The decoder layers under tensor parallelism with the fused cross-rank reduction: o_proj
+        and down_proj store each row of their partial product into the inbox of the rank that owns
+        the row (``linear_scatter``), and one ``tp_reduce_norm`` then sums the inbox into the
+        residual stream and leaves the next layer input h on every rank."""
         from .gpu import I32
         g, dm = self.gpu, self.cfg.dim
         tpk = g.kernel("tp_reduce_norm", [[self.tp_table.bytes], [dm], [t, dm]])
@@ -470,10 +482,10 @@ class Engine:
                 g.launch(att, [self.q, l.kc, l.vc, self.table, self.lens, self.o, scale])
                 if chunk_att is not None:
                     g.launch(chunk_att, [self.q, l.kc, l.vc, self.table, self.meta, self.o, scale])
-            g.launch(oproj, [self.o, l.wo, self.part])
+            g.launch(oproj, [self.o, l.wo, self.tp_table, I32(0)])
             g.launch(tpk, [self.tp_table, l.n2, self.x, eps, I32(0), I32(1), I32(self.nranks)])
             g.launch(gu, [self.h, l.wg, l.wu, self.mlp])
-            g.launch(down, [self.mlp, l.wd, self.part2])
+            g.launch(down, [self.mlp, l.wd, self.tp_table, I32(1)])
             last = i + 1 == len(self.layers)
             nxt = l.n2 if last else self.layers[i + 1].n1
             g.launch(tpk, [self.tp_table, nxt, self.x, eps, I32(1), I32(0 if last else 1), I32(self.nranks)])
