@@ -45,6 +45,7 @@ enum Kind : int {
   K_ARGMAX_MERGE,   // first maximum over the ranks' parts
   K_CHUNK_ATTENTION,  // causal attention of a prompt chunk's rows against the paged cache
   K_LINEAR_SCATTER,   // a tensor-parallel rank's partial product, each row stored into its owner rank's memory
+  K_LINEAR_ROPE_KV,   // the QKV projection with rope_q and kv_write as its epilogue
   K_COUNT
 };
 
@@ -54,6 +55,17 @@ enum Kind : int {
 struct MapEntry {
   uint64_t key[4];
   CUtensorMap m[3];
+};
+
+// linear_rope_kv: what the projection's epilogue needs beyond the product (kernels/llm.tl:78-112):
+// shapes fixed when the op is made, pointers taken from each launch's arguments.
+struct RopeArgs {
+  const int* pos = nullptr;
+  const int* slot = nullptr;
+  const float* Ct = nullptr;
+  const float* St = nullptr;
+  __half *Q = nullptr, *Kc = nullptr, *Vc = nullptr, *Kd = nullptr, *Vd = nullptr;
+  int H = 0, G = 0, D = 0, NPOS = 0, NS = 0;
 };
 
 struct Op {
@@ -69,6 +81,7 @@ struct Op {
   int p0 = 0, p1 = 0, p2 = 0, p3 = 0;
   // A scalar launch argument on its way into the kernel's parameters (linear_scatter: which inbox).
   int aux = 0;
+  RopeArgs rope;
   std::vector<MapEntry> maps;
 
   // The cached maps for `key`, or null; `fresh` returns a slot to fill (the cache is emptied

@@ -88,6 +88,7 @@ static const KindInfo KINDS[] = {
     {"argmax_merge", K_ARGMAX_MERGE, 2, 2},
     {"chunk_attention", K_CHUNK_ATTENTION, 6, 7},
     {"linear_scatter", K_LINEAR_SCATTER, 3, 4},
+    {"linear_rope_kv", K_LINEAR_ROPE_KV, 12, 12},
 };
 
 static std::string shape_text(const std::vector<int64_t>& s) {
@@ -112,7 +113,7 @@ static int profile_add(Ctx* c, const std::string& kernel) {
 
 static bool is_gemm(Kind k) {
   return k == K_LINEAR || k == K_LINEAR_RESIDUAL || k == K_LOGITS || k == K_GATE_UP || k == K_MATMUL ||
-         k == K_LINEAR_F32 || k == K_LINEAR_SCATTER;
+         k == K_LINEAR_F32 || k == K_LINEAR_SCATTER || k == K_LINEAR_ROPE_KV;
 }
 
 }  // namespace tb

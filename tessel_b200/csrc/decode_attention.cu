@@ -429,7 +429,12 @@ int make_decode(Ctx* c, Op& op) {
   const long long units = (long long)d.B * d.G * hgroups;
   long long want = (4LL * c->sm_count + units - 1) / units;
   if (const char* e = getenv("TB200_DECODE_SPLITS")) want = atoi(e);  // tuning and tests
-  const int max_split = (d.MP + 3) / 4;
+  int max_split = (d.MP + 3) / 4;
+  // Once every SM has a CTA or two anyway, more splits only shorten the tail, and a split costs
+  // its start-up (barriers, the first pages' latency) and a partial to merge: measured at 256
+  // sequences x 1 KV head (an 8-way tensor-parallel rank), two splits of 72 pages take 51 us,
+  // three of 48 pages 57 us, one 58 us. So there chunks stay 64 pages or longer.
+  if (units * 2 >= 3LL * c->sm_count && !getenv("TB200_DECODE_SPLITS")) max_split = d.MP >= 128 ? d.MP / 64 : 1;
   int nsplit = (int)(want < 1 ? 1 : (want > max_split ? max_split : want));
   int chunk = (d.MP + nsplit - 1) / nsplit;
   chunk = (chunk + 3) / 4 * 4;

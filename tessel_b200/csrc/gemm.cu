@@ -5,6 +5,11 @@
 //   gate_up          Y f16 = silu(X Wg^T) * (X Wu^T)   kernels/llm.tl:62-73
 //   matmul           C f16 = A B, B [K,N] row-major    kernels/matmul.tl:3-17
 //   linear_f32       Y f32 = X W^T (a tensor-parallel partial; no counterpart)
+//   linear_scatter   linear_f32 whose rows go to their owner ranks' memory (no counterpart)
+//   linear_rope_kv   the QKV projection with rope_q and kv_write (kernels/llm.tl:78-112) as its
+//                    epilogue: the rounded product is rotated and scattered into Q, the dense K and
+//                    V and the cache pages straight from the accumulators (no counterpart as one
+//                    kernel: the reference launches the three, src/llm/engine.rs:473-488)
 //
 // One CTA computes a (MT x 128) x BN tile of the output, MT in {1, 2}. Warp 0
 // streams 64-wide K slices of both operands into a shared-memory ring with TMA
@@ -40,7 +45,7 @@ namespace tb {
 
 namespace {
 
-enum Epi : int { EPI_F16 = 0, EPI_RESID = 1, EPI_F32 = 2, EPI_GATE_UP = 3 };
+enum Epi : int { EPI_F16 = 0, EPI_RESID = 1, EPI_F32 = 2, EPI_GATE_UP = 3, EPI_ROPE = 4 };
 
 constexpr int BM = 128, BK = 64;
 constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
@@ -64,6 +69,7 @@ struct GemmParams {
   void* out;
   int M, N, K, splits;
   unsigned int* status;
+  RopeArgs rope;
   // linear_scatter: row r goes to rank r % n's inbox `which`, at [this rank][r / n]; null otherwise.
   const TpTable* scatter;
   int which;
@@ -150,77 +156,139 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, int row, int co
   }
 }
 
+// One rotated pair (kernels/llm.tl:85-88): products and sums rounded separately, as the
+// interpreter does, so that the pages written from here are the reference's bits.
+__device__ __forceinline__ void rope_pair(float x1, float x2, float c, float s, float& y1, float& y2) {
+  y1 = __fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, s));
+  y2 = __fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, s));
+}
+
+__device__ __forceinline__ void store_h32(__half* dst, const float* v) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 o;
+    o.x = pack_h2(v[j], v[j + 1]);
+    o.y = pack_h2(v[j + 2], v[j + 3]);
+    o.z = pack_h2(v[j + 4], v[j + 5]);
+    o.w = pack_h2(v[j + 6], v[j + 7]);
+    *reinterpret_cast<uint4*>(dst + j) = o;
+  }
+}
+
+// linear_rope_kv: 32 columns of each half of one head of one row. `v1` holds columns
+// [32 hu, 32 hu + 32) of the head that starts at column `gc` of QKV, `v2` the same columns of
+// the head's second half. The product is rounded to f16 first (the reference's qkv buffer is
+// f16), stored to QKV, and then: a query head is rotated into Q; a key head is rotated into the
+// dense K and, unless the row's slot is outside the cache, its page; a value head is copied to
+// the dense V and its page.
+__device__ __forceinline__ void rope_store(const GemmParams& p, int row, int gc, int hu, float* v1, float* v2) {
+  const RopeArgs& a = p.rope;
+  const int D = a.D, d2 = D >> 1, HD = a.H * D, GD = a.G * D;
+  if (row >= p.M || gc >= p.N) return;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    v1[j] = __half2float(__float2half_rn(v1[j]));
+    v2[j] = __half2float(__float2half_rn(v2[j]));
+  }
+  const int off = hu * 32;
+  __half* qkv = (__half*)p.out + (size_t)row * p.N + gc + off;
+  store_h32(qkv, v1);
+  store_h32(qkv + d2, v2);
+  const int at = a.slot[row];
+  const bool keep = at >= 0 && at < a.NS;
+  if (gc >= HD + GD) {
+    const int g = (gc - HD - GD) / D;
+    __half* vd = a.Vd + ((size_t)row * a.G + g) * D + off;
+    store_h32(vd, v1);
+    store_h32(vd + d2, v2);
+    if (keep) {
+      __half* vc = a.Vc + ((size_t)at * a.G + g) * D + off;
+      store_h32(vc, v1);
+      store_h32(vc + d2, v2);
+    }
+    return;
+  }
+  const int ps = a.pos[row];
+  const bool in = ps >= 0 && ps < a.NPOS;
+  const float* ct = a.Ct + (size_t)(in ? ps : 0) * d2 + off;
+  const float* st = a.St + (size_t)(in ? ps : 0) * d2 + off;
+#pragma unroll
+  for (int j = 0; j < 32; j += 4) {
+    const float4 c = in ? *reinterpret_cast<const float4*>(ct + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 sn = in ? *reinterpret_cast<const float4*>(st + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float y1, y2;
+    rope_pair(v1[j], v2[j], c.x, sn.x, y1, y2), v1[j] = y1, v2[j] = y2;
+    rope_pair(v1[j + 1], v2[j + 1], c.y, sn.y, y1, y2), v1[j + 1] = y1, v2[j + 1] = y2;
+    rope_pair(v1[j + 2], v2[j + 2], c.z, sn.z, y1, y2), v1[j + 2] = y1, v2[j + 2] = y2;
+    rope_pair(v1[j + 3], v2[j + 3], c.w, sn.w, y1, y2), v1[j + 3] = y1, v2[j + 3] = y2;
+  }
+  if (gc < HD) {
+    __half* q = a.Q + ((size_t)row * a.H + gc / D) * D + off;
+    store_h32(q, v1);
+    store_h32(q + d2, v2);
+    return;
+  }
+  const int g = (gc - HD) / D;
+  __half* kd = a.Kd + ((size_t)row * a.G + g) * D + off;
+  store_h32(kd, v1);
+  store_h32(kd + d2, v2);
+  if (keep) {
+    __half* kc = a.Kc + ((size_t)at * a.G + g) * D + off;
+    store_h32(kc, v1);
+    store_h32(kc + d2, v2);
+  }
+}
+
 // The epilogue of one CTA: warps 2-9 read the CTA's MT x 128 rows of the finished accumulators
 // out of tensor memory (TMEM lane quadrant = warp % 4, one output row per thread; the two warps
-// of a quadrant take alternate 32-column chunks) and store them. With S > 1 the S CTAs that
-// split K first exchange partial tiles through distributed shared memory: the tile's 128 x 32
-// units are dealt round-robin to the splits, every CTA stores its partial of a unit into the
-// ring (idle by then) of the unit's owner, and the owner adds the partials in split order.
-// `split` is this CTA's index among the S; the CTA holding split s of the same tile has cluster
-// rank s * rank_stride + rank_off.
+// of a quadrant share the 32-column units between them) and store them. With S > 1 the S CTAs
+// that split K first exchange partial tiles through distributed shared memory: the tile's
+// 128 x 32 units are dealt to the splits in groups (a group is one unit, or for linear_rope_kv
+// the units of one head, which must meet in one CTA), every CTA stores its partial of a unit
+// into the ring (idle by then) of the unit's owner, and the owner adds the partials in split
+// order. `split` is this CTA's index among the S; the CTA holding split s of the same tile has
+// cluster rank s * rank_stride + rank_off.
 template <int MT, int BN, int NB, int EPI>
 __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem, unsigned char* smem,
                                               uint64_t* acc_full, int m0, int n0, int S, uint32_t split,
                                               uint32_t rank_stride, uint32_t rank_off) {
-  constexpr int UNITS = MT * (BN / 32);
+  constexpr int CH = BN / 32;
+  constexpr int UNITS = MT * CH;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool epi = warp >= 2;
   const int q = warp & 3;
   const int eh = (warp - 2) >> 2;
   const uint32_t lane_base = (uint32_t)(q * 32) << 16;
   const bool tracer = warp == 2 && lane == 0;
+  const int rit = q * 32 + lane;  // row within a 128-row block
+  // Units that stay together (one owner): a head for linear_rope_kv (BN is a multiple of D there).
+  const int UH = EPI == EPI_ROPE ? p.rope.D / 32 : 1;
+  const int groups = UNITS / UH;
+  const int per = ((groups + S - 1) / S) * UH;  // units each CTA owns, at most
+  auto owner_of = [&](int u) { return (uint32_t)((u / UH) % S); };
+  auto slot_of = [&](int u) { return ((u / UH) / S) * UH + u % UH; };
+  float* recv = (float*)smem;  // [(S - 1) senders][per][8 float4 columns][128 rows]
   if (epi) {
     pdl_wait();  // the epilogue reads and writes buffers other kernels touch
     mbar_wait(acc_full, 0, p.status, 203);
     tc_fence_after();
     if (tracer) TB_TRACE(4);
   }
-  if (S == 1) {
-    if (epi) {
-#pragma unroll 1
-      for (int mt = 0; mt < MT; ++mt) {
-        const int row = m0 + mt * BM + q * 32 + lane;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          if (((c0 >> 5) & 1) != eh) continue;
-          uint32_t r[32];
-          float v[32];
-          tmem_ld32(tmem + lane_base + mt * NB + c0, r);
-          if (EPI == EPI_GATE_UP) {
-            uint32_t r2[32];
-            tmem_ld32(tmem + lane_base + mt * NB + BN + c0, r2);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j]));
-          } else {
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          }
-          store_chunk<EPI>(p, row, n0 + c0, v, BN - c0 < 32 ? BN - c0 : 32);
-        }
-      }
-    }
-  } else {
+  if (S > 1) {
     // Split K: exchange partial tiles through distributed shared memory.
-    constexpr int CH = BN / 32;
-    const int per = UNITS / S;  // units each CTA owns (the host picks S dividing UNITS)
-    const uint32_t crank = split;
     __syncwarp();
     cluster_sync();  // every CTA of the cluster has finished its MMAs: all rings are free
     if (tracer) TB_TRACE(5);
-    float* recv = (float*)smem;  // [(S - 1) senders][per][8 float4 columns][128 rows]
-    const int rit = q * 32 + lane;  // row within the 128-row unit
     if (epi) {
       for (int u = 0; u < UNITS; ++u) {
-        const uint32_t owner = (uint32_t)(u % S);
-        if (owner == crank || ((u / S) & 1) != eh) continue;
+        const uint32_t owner = owner_of(u);
+        if (owner == split || (u & 1) != eh) continue;
         const int mt = u / CH, c0 = (u % CH) * 32;
         uint32_t r[32];
         tmem_ld32(tmem + lane_base + mt * NB + c0, r);
         tmem_ld_wait();
-        const uint32_t sidx = crank < owner ? crank : crank - 1;  // my place among the owner's senders
-        const uint32_t local = smem_u32(recv) + (sidx * per + u / S) * UNIT_BYTES + rit * 16;
+        const uint32_t sidx = split < owner ? split : split - 1;  // my place among the owner's senders
+        const uint32_t local = smem_u32(recv) + (sidx * per + slot_of(u)) * UNIT_BYTES + rit * 16;
         const uint32_t remote = cluster_map(local, owner * rank_stride + rank_off);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
@@ -232,43 +300,95 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem
     __syncwarp();
     cluster_sync();  // all partials have landed
     if (tracer) TB_TRACE(7);
-    if (epi) {
-      for (int slot = eh; slot < per; slot += 2) {
-        const int u = slot * S + (int)crank;
-        const int mt = u / CH, c0 = (u % CH) * 32;
-        uint32_t r[32];
-        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
-        tmem_ld_wait();
-        float v[32];
-        // Partials are added in rank order 0, 1, ..., S-1 whatever the timing.
-        for (int s = 0; s < S; ++s) {
-          if ((uint32_t)s == crank) {
+  }
+  // The 32 finished columns of unit u (owned by this CTA): the accumulator, plus, in split order
+  // 0, 1, ..., S-1 whatever the timing, the partials the other splits sent.
+  auto sum_unit = [&](int u, float* v) {
+    const int mt = u / CH, c0 = (u % CH) * 32;
+    uint32_t r[32];
+    tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+    tmem_ld_wait();
+    if (S == 1) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = s == 0 ? __uint_as_float(r[j]) : __fadd_rn(v[j], __uint_as_float(r[j]));
+      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      return;
+    }
+    const int slot = slot_of(u);
+    for (int s = 0; s < S; ++s) {
+      if ((uint32_t)s == split) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = s == 0 ? __uint_as_float(r[j]) : __fadd_rn(v[j], __uint_as_float(r[j]));
+      } else {
+        const int sidx = (uint32_t)s < split ? s : s - 1;
+        const float4* src = (const float4*)((const unsigned char*)recv + (sidx * per + slot) * UNIT_BYTES) + rit;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 t = src[j * 128];
+          if (s == 0) {
+            v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
           } else {
-            const int sidx = (uint32_t)s < crank ? s : s - 1;
-            const float4* src = (const float4*)((const unsigned char*)recv + (sidx * per + slot) * UNIT_BYTES) + rit;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 t = src[j * 128];
-              if (s == 0) {
-                v[4 * j] = t.x, v[4 * j + 1] = t.y, v[4 * j + 2] = t.z, v[4 * j + 3] = t.w;
-              } else {
-                v[4 * j] = __fadd_rn(v[4 * j], t.x);
-                v[4 * j + 1] = __fadd_rn(v[4 * j + 1], t.y);
-                v[4 * j + 2] = __fadd_rn(v[4 * j + 2], t.z);
-                v[4 * j + 3] = __fadd_rn(v[4 * j + 3], t.w);
-              }
-            }
+            v[4 * j] = __fadd_rn(v[4 * j], t.x);
+            v[4 * j + 1] = __fadd_rn(v[4 * j + 1], t.y);
+            v[4 * j + 2] = __fadd_rn(v[4 * j + 2], t.z);
+            v[4 * j + 3] = __fadd_rn(v[4 * j + 3], t.w);
           }
         }
-        store_chunk<EPI>(p, m0 + mt * BM + rit, n0 + c0, v);
       }
+    }
+  };
+  if (!epi) return;
+  if (EPI == EPI_ROPE) {
+    // Whole heads: a thread takes columns [32 hu, 32 hu + 32) of both halves of a head at a time.
+    int item = 0;
+    for (int gi = (int)split; gi < groups; gi += S) {
+      const int u0 = gi * UH, mt = u0 / CH, gc = n0 + (u0 % CH) * 32;
+      for (int hu = 0; hu < UH / 2; ++hu, ++item) {
+        if ((item & 1) != eh) continue;
+        float v1[32], v2[32];
+        sum_unit(u0 + hu, v1);
+        sum_unit(u0 + UH / 2 + hu, v2);
+        rope_store(p, m0 + mt * BM + rit, gc, hu, v1, v2);
+      }
+    }
+    return;
+  }
+  if (S == 1) {
+#pragma unroll 1
+    for (int mt = 0; mt < MT; ++mt) {
+      const int row = m0 + mt * BM + rit;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (((c0 >> 5) & 1) != eh) continue;
+        uint32_t r[32];
+        float v[32];
+        tmem_ld32(tmem + lane_base + mt * NB + c0, r);
+        if (EPI == EPI_GATE_UP) {
+          uint32_t r2[32];
+          tmem_ld32(tmem + lane_base + mt * NB + BN + c0, r2);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j]));
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        }
+        store_chunk<EPI>(p, row, n0 + c0, v, BN - c0 < 32 ? BN - c0 : 32);
+      }
+    }
+  } else {
+    int item = 0;
+    for (int gi = (int)split; gi < groups; gi += S, ++item) {
+      if ((item & 1) != eh) continue;
+      const int u = gi;  // groups are single units here
+      float v[32];
+      sum_unit(u, v);
+      store_chunk<EPI>(p, m0 + (u / CH) * BM + rit, n0 + (u % CH) * 32, v);
     }
   }
   // Rows stored into other GPUs' memory are acknowledged before this thread ends, so that the
   // kernel's completion (which the next kernel announces to those GPUs) covers them.
-  if (EPI == EPI_F32 && p.scatter != nullptr && epi) __threadfence_system();
+  if (EPI == EPI_F32 && p.scatter != nullptr) __threadfence_system();
 }
 
 // B_MN: B is a [K, N] row-major array (N-major operand); else W [N, K] (K-major).
@@ -577,6 +697,7 @@ __global__ void gemm_plain_kernel(const __half* __restrict__ A, const __half* __
 
 struct GemmShape {
   int M, N, K;
+  int D = 0;  // linear_rope_kv: head_dim (a tile must hold whole heads)
 };
 
 GemmShape gemm_shape(const Op& op) {
@@ -585,7 +706,8 @@ GemmShape gemm_shape(const Op& op) {
   g.M = (int)s[0][0];
   g.K = (int)s[0][1];
   g.N = op.kind == K_MATMUL ? (int)s[1][1] : (int)s[1][0];
-  return g;  // linear_scatter: X[M,K], W[N,K], table: the same two leading shapes
+  if (op.kind == K_LINEAR_ROPE_KV) g.D = (int)s[7][2];  // Q[T,H,D]
+  return g;  // linear_scatter, linear_rope_kv: X[M,K], W[N,K] lead as in linear
 }
 
 int epi_of(Kind k) {
@@ -597,6 +719,8 @@ int epi_of(Kind k) {
       return EPI_RESID;
     case K_GATE_UP:
       return EPI_GATE_UP;
+    case K_LINEAR_ROPE_KV:
+      return EPI_ROPE;
     default:
       return EPI_F32;
   }
@@ -658,6 +782,7 @@ int run(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, const voi
   p.status = c->status;
   p.scatter = op.kind == K_LINEAR_SCATTER ? (const TpTable*)out : nullptr;
   p.which = op.aux;
+  p.rope = op.rope;
   const dim3 grid((g.M + MT * BM - 1) / (MT * BM), (g.N + BN - 1) / BN, splits);
   TB_CUDA(c, launch_k(c, gemm_kernel<MT, BN, EPI, B_MN>, grid, dim3(GEMM_THREADS), Cfg::SMEM, splits, ma, mb, mb2, p));
   return 0;
@@ -707,6 +832,7 @@ int run_pair(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, cons
   p.status = c->status;
   p.scatter = op.kind == K_LINEAR_SCATTER ? (const TpTable*)out : nullptr;
   p.which = op.aux;
+  p.rope = op.rope;
   const dim3 grid(2 * ((g.M + 2 * BM - 1) / (2 * BM)), (g.N + BN - 1) / BN, splits);
   TB_CUDA(c, launch_kc(c, gemm_pair_kernel<BN, EPI>, grid, dim3(GEMM_THREADS), Cfg::SMEM, 2, splits, ma, mb, mb2, p));
   return 0;
@@ -722,6 +848,9 @@ int dispatch_pair(Ctx* c, Op& op, Kind kind, const GemmShape& g, int splits, con
       return run_pair<BN, EPI_F16>(c, op, g, splits, A, B, B2, out, attr_only);
     case EPI_RESID:
       return run_pair<BN, EPI_RESID>(c, op, g, splits, A, B, B2, out, attr_only);
+    case EPI_ROPE:
+      if constexpr (BN == 128 || BN == 256) return run_pair<BN, EPI_ROPE>(c, op, g, splits, A, B, B2, out, attr_only);
+      return fail(c, "gemm: linear_rope_kv pair tiles are 128 or 256 columns wide");
     default:
       return run_pair<BN, EPI_F32>(c, op, g, splits, A, B, B2, out, attr_only);
   }
@@ -747,6 +876,8 @@ int dispatch_epi(Ctx* c, Op& op, Kind kind, const GemmShape& g, int splits, cons
     if constexpr (BN >= 64 && BN != 192) return run<MT, BN, EPI_F16, true>(c, op, g, splits, A, B, B2, out, attr_only);
   } else if (epi == EPI_GATE_UP) {
     if constexpr (BN <= 128) return run<MT, BN, EPI_GATE_UP, false>(c, op, g, splits, A, B, B2, out, attr_only);
+  } else if (epi == EPI_ROPE) {
+    if constexpr (BN == 128 || BN == 256) return run<MT, BN, EPI_ROPE, false>(c, op, g, splits, A, B, B2, out, attr_only);
   } else if (epi == EPI_F16) {
     return run<MT, BN, EPI_F16, false>(c, op, g, splits, A, B, B2, out, attr_only);
   } else if (epi == EPI_RESID) {
@@ -786,6 +917,16 @@ struct Plan {
 const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
   const int epi = epi_of(kind);
   const int nk = (g.K + BK - 1) / BK;
+  // Units of the tile that one CTA must own together, and how many such groups a tile has.
+  const int uh = epi == EPI_ROPE ? g.D / 32 : 1;
+  if (epi == EPI_ROPE) {
+    if (bn != 128 && bn != 256) return "linear_rope_kv tiles are 128 or 256 columns wide";
+    if (g.D <= 0 || bn % g.D) return "a linear_rope_kv tile holds whole heads";
+  }
+  auto recv_fits = [&](int units, int stages, int stage) {
+    const int per = ((units / uh + s - 1) / s) * uh;
+    return (s - 1) * per * UNIT_BYTES <= stages * stage;
+  };
   if (mt == PAIR) {
     if (kind == K_MATMUL) return "CTA pairs take K-major weights only";
     if (bn != 128 && bn != 192 && bn != 256) return "pair tiles are 128, 192 or 256 columns wide";
@@ -798,8 +939,8 @@ const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
       const int units = bn / 32;
       if (epi == EPI_GATE_UP) return "gate_up does not split K";
       if (s > nk) return "more splits than 64-wide K blocks";
-      if (units % s) return "splits must divide the tile's 128 x 32 units";
-      if ((s - 1) * (units / s) * UNIT_BYTES > stages * stage) return "the partial tiles of the other splits do not fit the ring";
+      if ((units / uh) % s) return "splits must divide the tile's 128 x 32 units (its heads, for linear_rope_kv)";
+      if (!recv_fits(units, stages, stage)) return "the partial tiles of the other splits do not fit the ring";
     }
     return nullptr;
   }
@@ -820,8 +961,8 @@ const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
     const int units = mt * (bn / 32);
     if (epi == EPI_GATE_UP) return "gate_up does not split K";
     if (s > nk) return "more splits than 64-wide K blocks";
-    if (units % s) return "splits must divide the tile's 128 x 32 units";
-    if ((s - 1) * (units / s) * UNIT_BYTES > stages * stage) return "the partial tiles of the other splits do not fit the ring";
+    if ((units / uh) % s) return "splits must divide the tile's 128 x 32 units (its heads, for linear_rope_kv)";
+    if (!recv_fits(units, stages, stage)) return "the partial tiles of the other splits do not fit the ring";
   }
   return nullptr;
 }
@@ -843,7 +984,7 @@ std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
     if (mt == 2 && g.M <= BM) continue;
     for (int bn : bns) {
       for (int s = 1; s <= 4; s *= 2) {
-        if (plan_error(kind, g, mt, bn, s)) continue;
+        if (plan_error(kind, g, mt, bn, s)) continue;  // (leaves linear_rope_kv its 128- and 256-column tiles)
         if (s > 1 && nk < 8 * s) continue;
         const int nb = bn * nbf;
         const int stage = mt * BM * BK * 2 + nb * BK * 2;
@@ -897,10 +1038,27 @@ std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
 int make_gemm(Ctx* c, Op& op) {
   const auto& s = op.shapes;
   auto bad = [&](const char* why) { return fail(c, op.name + ": " + why); };
-  for (size_t i = 0; i < s.size(); ++i)
+  if (op.kind == K_LINEAR_ROPE_KV) {
+    // X[T,K], W[Wd,K], pos[T], slot[T], C, S [NPOS,D/2], QKV[T,Wd], Q[T,H,D], Kc, Vc [NS,G,D], K, V [T,G,D]
+    if (s[0].size() != 2 || s[1].size() != 2 || s[4].size() != 2 || s[6].size() != 2 || s[7].size() != 3 ||
+        s[8].size() != 3 || s[10].size() != 3)
+      return bad("shapes are X[T,K], W[Wd,K], pos[T], slot[T], C, S[NPOS,D/2], QKV[T,Wd], Q[T,H,D], Kc, Vc[NS,G,D], K, V[T,G,D]");
+    const int64_t T = s[0][0], Wd = s[1][0], H = s[7][1], D = s[7][2], G = s[8][1];
+    if (s[1][1] != s[0][1] || s[2][0] != T || s[3][0] != T || s[6][0] != T || s[6][1] != Wd || s[7][0] != T ||
+        s[5] != s[4] || s[9] != s[8] || s[11] != s[10] || s[8][2] != D || s[10][0] != T || s[10][1] != G ||
+        s[10][2] != D || s[4][1] != D / 2)
+      return bad("shapes disagree");
+    if (Wd != (H + 2 * G) * D) return bad("W must have (H + 2G) * D rows");
+    if (D != 64 && D != 128) return bad("head_dim must be 64 or 128 (use linear and rope_kv otherwise)");
+    if (s[0][1] <= 0 || s[0][1] % 8) return bad("K must be a positive multiple of 8 (use linear and rope_kv otherwise)");
+    op.rope.H = (int)H, op.rope.G = (int)G, op.rope.D = (int)D, op.rope.NPOS = (int)s[4][0], op.rope.NS = (int)s[8][0];
+  }
+  for (size_t i = 0; i < s.size() && op.kind != K_LINEAR_ROPE_KV; ++i)
     if (s[i].size() != 2 && !(op.kind == K_LINEAR_SCATTER && i == 2)) return bad("every array is two-dimensional");
   const GemmShape g = gemm_shape(op);
-  if (op.kind == K_LINEAR_SCATTER) {
+  if (op.kind == K_LINEAR_ROPE_KV) {
+    // checked above
+  } else if (op.kind == K_LINEAR_SCATTER) {
     if (s[1][1] != g.K || s[2].size() != 1 || (size_t)s[2][0] < sizeof(TpTable))
       return bad("shapes are X[M,K], W[N,K], table[bytes of tb200_tp_sizes]");
     if (g.K <= 0 || g.K % 8 || g.N % 4) return bad("K must be a positive multiple of 8 and N a multiple of 4");
@@ -946,6 +1104,13 @@ int launch_plan(Ctx* c, Op& op, const uint64_t* a, int mt, int bn, int splits) {
   if (op.kind == K_LINEAR_SCATTER) {
     op.aux = (int)(uint32_t)a[3];
     if (op.aux < 0 || op.aux > 1) return fail(c, op.name + ": which is 0 or 1");
+  }
+  if (op.kind == K_LINEAR_ROPE_KV) {
+    // X, W, pos, slot, C, S, QKV, Q, Kc, Vc, K, V
+    RopeArgs& r = op.rope;
+    r.pos = (const int*)a[2], r.slot = (const int*)a[3], r.Ct = (const float*)a[4], r.St = (const float*)a[5];
+    r.Q = (__half*)a[7], r.Kc = (__half*)a[8], r.Vc = (__half*)a[9], r.Kd = (__half*)a[10], r.Vd = (__half*)a[11];
+    return dispatch(c, op, op.kind, mt, bn, g, splits, (const void*)a[0], (const void*)a[1], nullptr, (void*)a[6], false);
   }
   const void* A = (const void*)a[0];
   const void* B = (const void*)a[1];

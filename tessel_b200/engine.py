@@ -156,6 +156,8 @@ class Engine:
         # new prompt length would pay for a tuning pass of its own.
         self.tune = True
         self.tune_rows = 256
+        # Run rope_q and kv_write as the epilogue of the QKV projection (head_dim 64 or 128).
+        self.fuse_rope = True
         # Replay decode steps as CUDA graphs (one launch instead of hundreds).
         self.graphs = True
         self._graph: Dict[tuple, int] = {}
@@ -408,10 +410,19 @@ class Engine:
         embed = k("embed", [[t], [v, dm], [t, dm]])
         norm = k("rmsnorm", [[t, dm], [dm], [t, dm]])
         l0 = self.layers[0]
-        qkv = self._mm("linear", [[t, dm], [w, dm], [t, w]], [self.h, l0.wqkv, self.qkv], t)
-        # rope_q and kv_write of the reference (src/llm/engine.rs:391-418) run as one launch.
-        ropekv = k("rope_kv", [[t, w], [t], [t], [npos, hd // 2], [npos, hd // 2], [t, nh, hd], [ns, ng, hd],
-                               [ns, ng, hd], [t, ng, hd], [t, ng, hd]])
+        rope_shapes = [[t], [t], [npos, hd // 2], [npos, hd // 2]]
+        kv_shapes = [[t, nh, hd], [ns, ng, hd], [ns, ng, hd], [t, ng, hd], [t, ng, hd]]
+        if self.fuse_rope and hd in (64, 128) and dm % 8 == 0:
+            # The QKV projection rotates and scatters its own output (src/llm/engine.rs:473-488 as
+            # one kernel): Q, the dense K and V and the cache pages come straight from the accumulators.
+            qkv = self._mm("linear_rope_kv", [[t, dm], [w, dm]] + rope_shapes + [[t, w]] + kv_shapes,
+                           [self.h, l0.wqkv, self.pos, self.slot, self.cos, self.sin, self.qkv, self.q, l0.kc, l0.vc,
+                            self.k, self.v], t)
+            ropekv = None
+        else:
+            qkv = self._mm("linear", [[t, dm], [w, dm], [t, w]], [self.h, l0.wqkv, self.qkv], t)
+            # rope_q and kv_write of the reference (src/llm/engine.rs:391-418) run as one launch.
+            ropekv = k("rope_kv", [[t, w]] + rope_shapes + kv_shapes)
         if prefill:
             att = k("prefill_attention", [[t, nh, hd], [t, ng, hd], [t, ng, hd], [t], [t, nh, hd]])
         else:
@@ -450,8 +461,7 @@ class Engine:
             return
         for l in self.layers:
             g.launch(norm, [self.x, l.n1, self.h, eps])
-            g.launch(qkv, [self.h, l.wqkv, self.qkv])
-            g.launch(ropekv, [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l.kc, l.vc, self.k, self.v])
+            self._launch_qkv(qkv, ropekv, l)
             if prefill:
                 g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
             else:
@@ -464,6 +474,17 @@ class Engine:
             project(down, self.mlp, l.wd)
         self._launch_head(t, bw, greedy, eps)
 
+    def _launch_qkv(self, qkv: K, ropekv: Optional[K], l: _DevLayer) -> None:
+        """QKV projection, rotary embedding and the KV-cache write of one layer: one kernel, or
+        (``ropekv`` given) the projection followed by ``rope_kv``."""
+        g = self.gpu
+        if ropekv is None:
+            g.launch(qkv, [self.h, l.wqkv, self.pos, self.slot, self.cos, self.sin, self.qkv, self.q, l.kc, l.vc,
+                           self.k, self.v])
+            return
+        g.launch(qkv, [self.h, l.wqkv, self.qkv])
+        g.launch(ropekv, [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l.kc, l.vc, self.k, self.v])
+
     def _launch_layers_fused(self, t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale, chunk_att=None) -> None:
         """The decoder layers under tensor parallelism with the fused cross-rank reduction: o_proj
         and down_proj store each row of their partial product into the inbox of the rank that owns
@@ -474,8 +495,7 @@ class Engine:
         tpk = g.kernel("tp_reduce_norm", [[self.tp_table.bytes], [dm], [t, dm]])
         g.launch(norm, [self.x, self.layers[0].n1, self.h, eps])
         for i, l in enumerate(self.layers):
-            g.launch(qkv, [self.h, l.wqkv, self.qkv])
-            g.launch(ropekv, [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l.kc, l.vc, self.k, self.v])
+            self._launch_qkv(qkv, ropekv, l)
             if prefill:
                 g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
             else:

@@ -3,6 +3,7 @@
     python -m tessel_b200.microbench decode [--seqs 256 --ctx-lo 512 --ctx-hi 2304 --heads 32 --kv-heads 8 --dim 128]
     python -m tessel_b200.microbench gemm   [--m 4096 --n 4096 --k 4096] [--kind matmul|linear|gate_up|linear_residual]
     python -m tessel_b200.microbench flash  [--heads 256 --seq 4096 --dim 128]
+    python -m tessel_b200.microbench flash --packed [--prompts 8 --seq 4096 --heads 32 --kv-heads 8 --dim 128]
 
 Each prints one JSON line: the mean device time per launch (CUDA events on the launching
 stream, one pair per iteration, after warm-up; a 256 MB buffer is overwritten between
@@ -147,6 +148,28 @@ def flash(gpu, torch, heads=256, seq=4096, dim=128, iters=10, seed=0):
             "frac_tensor": flops / (mean * 1e-3) / 1e12 / tf, "peak_kind": kindp}
 
 
+def flash_packed(gpu, torch, prompts=8, seq=4096, heads=32, kv_heads=32, dim=128, iters=10, seed=0):
+    """Benchmark configuration 3 in the engine's own form: `prompts` prompts of `seq` tokens packed
+    into one step of `prefill_attention` (Q/O [S,H,D], K/V [S,G,D], per-row starts)."""
+    from .gpu import Buf, F32
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    S = prompts * seq
+    q = torch.empty((S, heads, dim), dtype=torch.float16, device="cuda").normal_(generator=gen)
+    k, v = (torch.empty((S, kv_heads, dim), dtype=torch.float16, device="cuda").normal_(generator=gen) for _ in range(2))
+    o = torch.zeros_like(q)
+    starts = (torch.arange(S, dtype=torch.int32, device="cuda") // seq) * seq
+    kern = gpu.kernel("prefill_attention", [list(q.shape), list(k.shape), list(v.shape), [S], list(q.shape)])
+    args = [Buf(t.data_ptr(), t.numel() * t.element_size()) for t in (q, k, v, starts, o)] + [F32(1 / math.sqrt(dim))]
+    t = Timer(gpu, torch)
+    mean, best = t.run(lambda: gpu.launch(kern, args), iters)
+    flops = 2.0 * 2.0 * prompts * heads * seq * seq * dim / 2.0
+    _, tf, kindp = _peaks()
+    return {"kernel": "prefill_attention", "prompts": prompts, "seq": seq, "heads": heads, "kv_heads": kv_heads,
+            "head_dim": dim, "ms": mean, "ms_min": best, "flops": flops, "tflops": flops / (mean * 1e-3) / 1e12,
+            "peak_tflops": tf, "frac_tensor": flops / (mean * 1e-3) / 1e12 / tf, "peak_kind": kindp}
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -161,6 +184,10 @@ def main():
     f = sub.add_parser("flash")
     for name, default in (("heads", 256), ("seq", 4096), ("dim", 128), ("iters", 10)):
         f.add_argument("--" + name, type=int, default=default)
+    f.add_argument("--packed", action="store_true",
+                   help="the packed prefill form: --prompts prompts of --seq tokens, --heads query heads on --kv-heads")
+    f.add_argument("--prompts", type=int, default=8)
+    f.add_argument("--kv-heads", type=int, default=0)
     a = ap.parse_args()
     import torch
     if not torch.cuda.is_available():
@@ -171,6 +198,9 @@ def main():
         r = decode(gpu, torch, a.seqs, a.ctx_lo, a.ctx_hi, a.heads, a.kv_heads, a.dim, a.iters)
     elif a.cmd == "gemm":
         r = gemm(gpu, torch, a.m, a.n, a.k, a.kind, a.iters)
+    elif a.packed:
+        heads = 32 if a.heads == 256 else a.heads
+        r = flash_packed(gpu, torch, a.prompts, a.seq, heads, a.kv_heads or heads, a.dim, a.iters)
     else:
         r = flash(gpu, torch, a.heads, a.seq, a.dim, a.iters)
     print(json.dumps(r), flush=True)

@@ -129,6 +129,14 @@ class EmuGpu:
             kc, vc, kd, vd = oracle.kv_write(A(0, h), A(1, i), A(2, i), A(3, f), A(4, f), A(6, h), A(7, h), sh[6][1],
                                              sh[6][2])
             A(6, h)[:], A(7, h)[:], A(8, h)[:], A(9, h)[:] = kc, vc, kd, vd
+        elif name == "linear_rope_kv":
+            # X, W, pos, slot, C, S, QKV, Q, Kc, Vc, K, V: linear, rope_q and kv_write in a row.
+            qkv = oracle.linear(A(0, h), A(1, h))
+            A(6, h)[:] = qkv
+            A(7, h)[:] = oracle.rope_q(qkv, A(2, i), A(4, f), A(5, f), sh[7][1], sh[7][2])
+            kc, vc, kd, vd = oracle.kv_write(qkv, A(2, i), A(3, i), A(4, f), A(5, f), A(8, h), A(9, h), sh[8][1],
+                                             sh[8][2])
+            A(8, h)[:], A(9, h)[:], A(10, h)[:], A(11, h)[:] = kc, vc, kd, vd
         elif name == "prefill_attention":
             A(4, h)[:] = oracle.prefill_attention(A(0, h), A(1, h), A(2, h), A(3, i), sc(5))
         elif name == "flash_attention":

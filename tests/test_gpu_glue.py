@@ -89,6 +89,42 @@ def test_rope_q_and_kv_write_bit_exact(gpu, T, H, G, D, NPOS):
         assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
 
 
+@pytest.mark.parametrize("plan,T,K,H,G,D", [
+    (None, 256, 512, 32, 8, 128),            # the Llama-3-8B heads, whatever tile the library picks
+    ("2,256,1", 250, 264, 4, 2, 128), ("1,128,1", 100, 136, 6, 1, 64), ("2,128,2", 256, 1032, 6, 2, 64),
+    ("2,256,2", 256, 1040, 4, 2, 128), ("3,256,1", 256, 520, 8, 4, 64), ("3,128,1", 200, 272, 5, 1, 128),
+    ("3,256,2", 256, 2056, 12, 2, 128), ("3,128,2", 256, 1096, 6, 1, 64), ("1,256,4", 128, 2048, 8, 4, 64),
+])
+def test_projection_with_rope_and_kv_write_as_its_epilogue(gpu, monkeypatch, plan, T, K, H, G, D):
+    """linear_rope_kv: the product it stores is `linear`'s (within tolerance of the oracle), and
+    Q, the dense K and V and the cache pages are exactly what the oracle's rope_q and kv_write make
+    of THAT product - bit for bit, through every tile, the CTA-pair kernel and the split-K exchange
+    (whose unit ownership goes by heads here); dropped writes and positions outside the tables
+    included."""
+    if plan:
+        monkeypatch.setenv("TB200_GEMM_PLAN", plan)
+    r = oracle.Rng(6)
+    W = (H + 2 * G) * D
+    NPOS, P = 96, 16
+    NS = P * ((T + 15) // 16 + 3)
+    x, w = r.tensor(h, (T, K)), r.tensor(h, (W, K), 0.1)
+    pos = ((np.arange(T) * 7) % NPOS).astype(i32)
+    pos[-1] = NPOS
+    Ct, St = oracle.rope_tables(NPOS, D, 10000.0)
+    slot = np.random.default_rng(1).permutation(NS)[:T].astype(i32)
+    slot[-2:] = NS
+    slot[0] = -5
+    kc0, vc0 = r.tensor(h, (NS, G, D)), r.tensor(h, (NS, G, D))
+    z = lambda *shape: np.zeros(shape, h)
+    qkv, q, kc, vc, kd, vd = run(gpu, "linear_rope_kv", [x, w, pos, slot, Ct, St, z(T, W), z(T, H, D), kc0, vc0,
+                                                         z(T, G, D), z(T, G, D)], [6, 7, 8, 9, 10, 11])
+    assert rel_err(qkv, oracle.linear(x, w)) <= TOL
+    assert np.array_equal(q.view(np.uint16), oracle.rope_q(qkv, pos, Ct, St, H, D).view(np.uint16))
+    wkc, wvc, wkd, wvd = oracle.kv_write(qkv, pos, slot, Ct, St, kc0, vc0, G, D)
+    for name, got, want in (("Kc", kc, wkc), ("Vc", vc, wvc), ("K", kd, wkd), ("V", vd, wvd)):
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), name
+
+
 def test_residual_add_and_argmax(gpu):
     r = oracle.Rng(5)
     a, b = r.tensor(f, (64, 512)), r.tensor(f, (64, 512))

@@ -92,6 +92,32 @@ def test_config3_shape_sampled(gpu):
         assert rel_err(got[hh, rows], want[0, rows]) <= TOL
 
 
+@pytest.mark.parametrize("G", [32, 8])
+def test_config3_packed_form_sampled(gpu, G):
+    """benchmark configuration 3 as the engine runs it: 8 prompts of 4096 tokens packed into one
+    step (S = 32768, per-row starts), 32 query heads on 32 or 8 KV heads, D 128. Sampled 64-row
+    blocks (the first and last of a prompt, one that a prompt boundary cuts just before) against
+    the oracle; and the first row of every prompt attends to itself only, so O == V there."""
+    g = np.random.default_rng(7)
+    H, D, n, L = 32, 128, 8, 4096
+    S = n * L
+    q = g.standard_normal((S, H, D), dtype=f).astype(h)
+    k, v = g.standard_normal((S, G, D), dtype=f).astype(h), g.standard_normal((S, G, D), dtype=f).astype(h)
+    st = starts_of([L] * n, S)
+    scale = float(1.0 / np.sqrt(D))
+    got = prefill(gpu, q, k, v, st, scale)
+    first = np.arange(n) * L
+    rep = H // G
+    assert np.array_equal(got[first].view(np.uint16), np.repeat(v[first], rep, axis=1).view(np.uint16))
+    for blk in (0, L // 64 - 1, L // 64, 3 * L // 64 + 17, S // 64 - 1):
+        rows = slice(blk * 64, blk * 64 + 64)
+        lo = int(st[blk * 64])
+        # The block's rows see keys [lo, blk * 64 + 64) only: the oracle on that window.
+        w0, w1 = lo, blk * 64 + 64
+        want = oracle.prefill_attention(q[w0:w1], k[w0:w1], v[w0:w1], (st[w0:w1] - lo).astype(i32), scale)
+        assert rel_err(got[rows], want[-64:]) <= TOL, blk
+
+
 @pytest.mark.parametrize("H,G,D,P,T,chunks", [
     # (row0, nrows, pos0): rows of the step, tokens at positions pos0 ... of their sequence
     (32, 8, 128, 16, 512, [(3, 300, 77), (303, 5, 0), (310, 128, 512)]),   # several 256-row CTAs; a start mid-page
