@@ -51,6 +51,7 @@ constexpr int BM = 128, BK = 64;
 constexpr int GEMM_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
 constexpr int UNIT_BYTES = 128 * 32 * 4;  // one 128-row x 32-column f32 unit of a partial tile
 constexpr int PAIR = 3;                   // plan code of the CTA-pair kernel (where MT is 1 or 2 otherwise)
+constexpr int SCATTER_STAGE_BYTES = 8 * 4096;  // linear_scatter: 4 KB per epilogue warp, at the end of the ring
 
 #ifdef TB200_TRACE
 __device__ unsigned long long* g_trace = nullptr;  // [CTA][16] timestamps (ns), development builds only
@@ -99,6 +100,38 @@ struct GemmCfg {
   static_assert(BN % 32 == 0 || EPI == EPI_GATE_UP, "only gate_up has a ragged last chunk");
   static_assert(STAGES >= 2, "ring too shallow");
 };
+
+// linear_scatter: 32 columns of 32 rows (one per lane) into the owner ranks' inboxes. A thread
+// holds a row, and a row's owner is another GPU more often than not: storing straight from the
+// registers would cross NVLink as 16-byte pieces of 32 different rows per instruction, which
+// measured 17 us on top of a 22 us projection. So the warp turns the 32 x 32 block round in 4 KB
+// of shared memory (chunks XOR-swizzled by row: no bank conflicts either way) and stores row by
+// row, 128 contiguous bytes per instruction.
+__device__ __forceinline__ void scatter_store(const GemmParams& p, float* stage, int row, int col0, const float* v) {
+  const int lane = threadIdx.x & 31;
+  float4* sw = reinterpret_cast<float4*>(stage);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sw[lane * 8 + (j ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  __syncwarp();
+  const int row0 = row - lane;
+  const bool col_ok = col0 + lane < p.N;
+  // Consecutive rows go round the owners: no division per row.
+  const TpTable* t = p.scatter;
+  const int n = t->nranks, per = (p.M + n - 1) / n;
+  int owner = row0 % n;
+  size_t at = ((size_t)t->rank * per + row0 / n) * p.N + col0 + lane;  // offset in the owner's inbox
+  float* const* inbox = t->part[p.which];
+#pragma unroll 4
+  for (int r = 0; r < 32; ++r) {
+    const float val = stage[r * 32 + (((lane >> 2) ^ (r & 7)) << 2) + (lane & 3)];
+    if (row0 + r < p.M && col_ok) inbox[owner][at] = val;
+    if (++owner == n) {
+      owner = 0;
+      at += p.N;
+    }
+  }
+  __syncwarp();
+}
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
   // g / (1 + exp(-g)) * u (kernels/llm.tl:73) on the fast exponential and division units:
@@ -251,7 +284,7 @@ __device__ __forceinline__ void rope_store(const GemmParams& p, int row, int gc,
 template <int MT, int BN, int NB, int EPI>
 __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem, unsigned char* smem,
                                               uint64_t* acc_full, int m0, int n0, int S, uint32_t split,
-                                              uint32_t rank_stride, uint32_t rank_off) {
+                                              uint32_t rank_stride, uint32_t rank_off, int ring_bytes) {
   constexpr int CH = BN / 32;
   constexpr int UNITS = MT * CH;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -268,6 +301,10 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem
   auto owner_of = [&](int u) { return (uint32_t)((u / UH) % S); };
   auto slot_of = [&](int u) { return ((u / UH) / S) * UH + u % UH; };
   float* recv = (float*)smem;  // [(S - 1) senders][per][8 float4 columns][128 rows]
+  // linear_scatter: 4 KB per epilogue warp at the end of the ring (idle by now; the received
+  // partials sit at its start), to turn blocks round before they leave for other GPUs.
+  float* turn = (float*)(smem + ring_bytes - SCATTER_STAGE_BYTES) + (warp - 2) * 1024;
+  const bool scatter = EPI == EPI_F32 && p.scatter != nullptr;
   if (epi) {
     pdl_wait();  // the epilogue reads and writes buffers other kernels touch
     mbar_wait(acc_full, 0, p.status, 203);
@@ -373,7 +410,10 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         }
-        store_chunk<EPI>(p, row, n0 + c0, v, BN - c0 < 32 ? BN - c0 : 32);
+        if (scatter)
+          scatter_store(p, turn, row, n0 + c0, v);
+        else
+          store_chunk<EPI>(p, row, n0 + c0, v, BN - c0 < 32 ? BN - c0 : 32);
       }
     }
   } else {
@@ -383,12 +423,12 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem
       const int u = gi;  // groups are single units here
       float v[32];
       sum_unit(u, v);
-      store_chunk<EPI>(p, m0 + (u / CH) * BM + rit, n0 + (u % CH) * 32, v);
+      if (scatter)
+        scatter_store(p, turn, m0 + (u / CH) * BM + rit, n0 + (u % CH) * 32, v);
+      else
+        store_chunk<EPI>(p, m0 + (u / CH) * BM + rit, n0 + (u % CH) * 32, v);
     }
   }
-  // Rows stored into other GPUs' memory are acknowledged before this thread ends, so that the
-  // kernel's completion (which the next kernel announces to those GPUs) covers them.
-  if (EPI == EPI_F32 && p.scatter != nullptr) __threadfence_system();
 }
 
 // B_MN: B is a [K, N] row-major array (N-major operand); else W [N, K] (K-major).
@@ -493,7 +533,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   }
 
-  tile_epilogue<MT, BN, NB, EPI>(p, tmem, smem, acc_full, m0, n0, S, S > 1 ? cluster_ctarank() : 0u, 1u, 0u);
+  tile_epilogue<MT, BN, NB, EPI>(p, tmem, smem, acc_full, m0, n0, S, S > 1 ? cluster_ctarank() : 0u, 1u, 0u, Cfg::BAR_OFF);
   const bool tracer = warp == 2 && lane == 0;
   if (tracer) TB_TRACE(8);
   tc_fence_before();
@@ -628,7 +668,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   }
   __syncwarp();
-  tile_epilogue<1, BN, Cfg::NB, EPI>(p, tmem, smem, acc_full, m0, n0, S, crank >> 1, 2u, half);
+  tile_epilogue<1, BN, Cfg::NB, EPI>(p, tmem, smem, acc_full, m0, n0, S, crank >> 1, 2u, half, Cfg::BAR_OFF);
   if (warp == 2 && (threadIdx.x & 31) == 0) TB_TRACE(8);
   // Both CTAs have read their accumulators (and every barrier signal of the pair has landed)
   // before either frees tensor memory or leaves.
@@ -925,7 +965,8 @@ const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
   }
   auto recv_fits = [&](int units, int stages, int stage) {
     const int per = ((units / uh + s - 1) / s) * uh;
-    return (s - 1) * per * UNIT_BYTES <= stages * stage;
+    // linear_scatter keeps the end of the ring for turning blocks round before they are stored.
+    return (s - 1) * per * UNIT_BYTES <= stages * stage - (kind == K_LINEAR_SCATTER ? SCATTER_STAGE_BYTES : 0);
   };
   if (mt == PAIR) {
     if (kind == K_MATMUL) return "CTA pairs take K-major weights only";

@@ -37,9 +37,10 @@
 // reading in this one. Nobody reads another rank's x, h or inbox.
 //
 // Step 1's signal is a relaxed store: what it announces was written by the PREVIOUS kernel of
-// the stream, whose threads fenced their remote stores before they ended, and a kernel's writes
-// are complete when its successor starts (the stream order; with programmatic dependent launch,
-// after griddepcontrol.wait).
+// the stream, and a kernel's writes, those into a peer's memory included, are complete when its
+// successor starts (the stream order; with programmatic dependent launch, after
+// griddepcontrol.wait, which returns only once the earlier grid has finished and its memory
+// operations are performed).
 #include "common.cuh"
 
 namespace tb {
