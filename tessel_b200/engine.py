@@ -156,8 +156,12 @@ class Engine:
         # new prompt length would pay for a tuning pass of its own.
         self.tune = True
         self.tune_rows = 256
-        # Run rope_q and kv_write as the epilogue of the QKV projection (head_dim 64 or 128).
-        self.fuse_rope = True
+        # Run rope_q and kv_write as the epilogue of the QKV projection (head_dim 64 or 128): True,
+        # False, or None = decide per step size by timing both forms on the device (where tuning
+        # is on; elsewhere fuse when the projection is at least 2048 columns wide: a narrow one,
+        # such as an 8-way tensor-parallel rank's, has too few whole-head tiles to fill the SMs).
+        self.fuse_rope: Optional[bool] = None
+        self._fuse_by_rows: Dict[int, bool] = {}
         # Replay decode steps as CUDA graphs (one launch instead of hundreds).
         self.graphs = True
         self._graph: Dict[tuple, int] = {}
@@ -396,6 +400,40 @@ class Engine:
             tuned[kern.id] = g.tune(kern, args)
         return kern
 
+    def _fuse_rope_for(self, t: int, fused_shapes, fused_args, rope_shapes, kv_shapes) -> bool:
+        """Whether steps of ``t`` rows run the QKV projection with rope_q / kv_write as its
+        epilogue (one kernel) or as projection + ``rope_kv`` (two). Undecided (``fuse_rope`` is
+        None) and able to time kernels: both forms are timed once on the engine's buffers, before
+        the step's own launches rewrite what they wrote, and the faster is kept."""
+        cfg, g = self.cfg, self.gpu
+        w, dm, hd = cfg.qkv(), cfg.dim, cfg.head_dim
+        if hd not in (64, 128) or dm % 8:
+            return False
+        if self.fuse_rope is not None:
+            return self.fuse_rope
+        if t in self._fuse_by_rows:
+            return self._fuse_by_rows[t]
+        choice = w >= 2048
+        if self.tune and t <= self.tune_rows and getattr(g, "tuned", None) is not None:
+            l0 = self.layers[0]
+            kf, kp = g.kernel("linear_rope_kv", fused_shapes), g.kernel("linear", [[t, dm], [w, dm], [t, w]])
+            g.tuned[kf.id] = g.tune(kf, fused_args)
+            g.tuned[kp.id] = g.tune(kp, [self.h, l0.wqkv, self.qkv])
+            fused_us, plain_us = g.tuned[kf.id][1], g.tuned[kp.id][1]
+            rk = g.kernel("rope_kv", [[t, w]] + rope_shapes + kv_shapes)
+            args = [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l0.kc, l0.vc, self.k, self.v]
+            for _ in range(2):
+                g.launch(rk, args)
+            g.sync()
+            g.time_begin()
+            for _ in range(8):
+                g.launch(rk, args)
+            rope_us = g.time_end() * 1000.0 / 8
+            if fused_us > 0 and plain_us > 0:
+                choice = fused_us < plain_us + rope_us
+        self._fuse_by_rows[t] = choice
+        return choice
+
     def launch_all(self, t: int, prefill: bool, bw: Optional[int], greedy: bool = False) -> None:
         """Launches one step's kernels for ``t`` rows: the decoder, then, for ``bw`` rows of
         logits, the final norm and the LM head (and the token choice when ``greedy``)."""
@@ -412,12 +450,13 @@ class Engine:
         l0 = self.layers[0]
         rope_shapes = [[t], [t], [npos, hd // 2], [npos, hd // 2]]
         kv_shapes = [[t, nh, hd], [ns, ng, hd], [ns, ng, hd], [t, ng, hd], [t, ng, hd]]
-        if self.fuse_rope and hd in (64, 128) and dm % 8 == 0:
+        fused_shapes = [[t, dm], [w, dm]] + rope_shapes + [[t, w]] + kv_shapes
+        fused_args = [self.h, l0.wqkv, self.pos, self.slot, self.cos, self.sin, self.qkv, self.q, l0.kc, l0.vc,
+                      self.k, self.v]
+        if self._fuse_rope_for(t, fused_shapes, fused_args, rope_shapes, kv_shapes):
             # The QKV projection rotates and scatters its own output (src/llm/engine.rs:473-488 as
             # one kernel): Q, the dense K and V and the cache pages come straight from the accumulators.
-            qkv = self._mm("linear_rope_kv", [[t, dm], [w, dm]] + rope_shapes + [[t, w]] + kv_shapes,
-                           [self.h, l0.wqkv, self.pos, self.slot, self.cos, self.sin, self.qkv, self.q, l0.kc, l0.vc,
-                            self.k, self.v], t)
+            qkv = self._mm("linear_rope_kv", fused_shapes, fused_args, t)
             ropekv = None
         else:
             qkv = self._mm("linear", [[t, dm], [w, dm], [t, w]], [self.h, l0.wqkv, self.qkv], t)

@@ -3,6 +3,7 @@
     python -m tessel_b200.microbench decode [--seqs 256 --ctx-lo 512 --ctx-hi 2304 --heads 32 --kv-heads 8 --dim 128]
     python -m tessel_b200.microbench gemm   [--m 4096 --n 4096 --k 4096] [--kind matmul|linear|gate_up|linear_residual]
     python -m tessel_b200.microbench flash  [--heads 256 --seq 4096 --dim 128]
+    python -m tessel_b200.microbench chunked [--prompt 4096 --chunk 512 --layers 4]
     python -m tessel_b200.microbench flash --packed [--prompts 8 --seq 4096 --heads 32 --kv-heads 8 --dim 128]
 
 Each prints one JSON line: the mean device time per launch (CUDA events on the launching
@@ -170,6 +171,38 @@ def flash_packed(gpu, torch, prompts=8, seq=4096, heads=32, kv_heads=32, dim=128
             "peak_tflops": tf, "frac_tensor": flops / (mean * 1e-3) / 1e12 / tf, "peak_kind": kindp}
 
 
+def chunked(gpu, torch, prompt=4096, chunk=512, layers=4, seed=0):
+    """Prefill of one `prompt`-token prompt on a `layers`-layer Llama-3-8B-shaped model: in one
+    step, and fed `chunk` tokens at a time through the mixed steps (chunk_attention over the paged
+    cache). Wall-clock tokens/s of each, after a warm-up run of the same thing."""
+    import time
+    from .engine import Engine, Limits
+    from .model import Config
+    from .sched import Request, generate_with
+    from .synth import device_weights
+    cfg = Config.llama3_8b(max_pos=prompt + 64)
+    cfg = Config(**{**cfg.__dict__, "layers": layers, "vocab": 16032})
+    w = device_weights(cfg, 0, 1, torch)
+    g = np.random.default_rng(seed)
+    toks = g.integers(0, cfg.vocab, prompt).tolist()
+    pages = -(-(prompt + 8) // 16) + 4
+    out = {"kernel": "chunked_prefill", "prompt": prompt, "chunk": chunk, "layers": layers}
+    for name, max_tokens, ch in (("one_step", prompt, 0), ("chunked", chunk, chunk)):
+        e = Engine(gpu, w, Limits(page=16, pages=pages, max_tokens=max_tokens, max_seq_pages=pages), sharded=True)
+        best = None
+        for _ in range(3):
+            gpu.sync()
+            t0 = time.perf_counter()
+            outs, st = generate_with(e, [Request(toks, 1)], 1, True, device_argmax=True, chunk=ch)
+            gpu.sync()
+            dt = time.perf_counter() - t0
+            best = dt if best is None else min(best, dt)
+        out[name] = {"seconds": best, "tok_s": prompt / best, "first_token": int(outs[0].tokens[0])}
+    out["chunked_over_one_step"] = out["chunked"]["tok_s"] / out["one_step"]["tok_s"]
+    out["same_first_token"] = out["chunked"]["first_token"] == out["one_step"]["first_token"]
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -188,6 +221,9 @@ def main():
                    help="the packed prefill form: --prompts prompts of --seq tokens, --heads query heads on --kv-heads")
     f.add_argument("--prompts", type=int, default=8)
     f.add_argument("--kv-heads", type=int, default=0)
+    ck = sub.add_parser("chunked")
+    for name, default in (("prompt", 4096), ("chunk", 512), ("layers", 4)):
+        ck.add_argument("--" + name, type=int, default=default)
     a = ap.parse_args()
     import torch
     if not torch.cuda.is_available():
@@ -198,6 +234,8 @@ def main():
         r = decode(gpu, torch, a.seqs, a.ctx_lo, a.ctx_hi, a.heads, a.kv_heads, a.dim, a.iters)
     elif a.cmd == "gemm":
         r = gemm(gpu, torch, a.m, a.n, a.k, a.kind, a.iters)
+    elif a.cmd == "chunked":
+        r = chunked(gpu, torch, a.prompt, a.chunk, a.layers)
     elif a.packed:
         heads = 32 if a.heads == 256 else a.heads
         r = flash_packed(gpu, torch, a.prompts, a.seq, heads, a.kv_heads or heads, a.dim, a.iters)
