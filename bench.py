@@ -50,10 +50,11 @@ sys.path.insert(0, ROOT)
 METRIC = "decode_tokens_per_s"
 UNIT = "tok/s"
 # DRAM bytes moved per algorithmic byte by the decode-attention kernel, from a profiler capture
-# (dram__bytes_read + dram__bytes_write) of a smaller batch of the same shape: 295.82 MB read
-# and 5.00 MB written for 294.72 MB of algorithmic bytes; traffic grows in proportion to the
-# sequences processed, so the ratio carries to a full launch.
-DRAM_PER_ALGORITHMIC_BYTE = (295.82 + 5.00) / 294.72
+# (dram__bytes_read + dram__bytes_write) of ONE launch of the same one-split form on a batch that
+# fits the profiler's size rule: 256 sequences at contexts U[256, 768] (2048 CTAs, 0.55 GB):
+# 558.32 MB read and 4.73 MB written for 552.52 MB of algorithmic bytes. Traffic grows in
+# proportion to the KV bytes read, so the ratio carries to the benchmark's launch.
+DRAM_PER_ALGORITHMIC_BYTE = (558.32 + 4.73) / 552.52
 
 
 def parse():

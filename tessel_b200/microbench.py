@@ -3,7 +3,7 @@
     python -m tessel_b200.microbench decode [--seqs 256 --ctx-lo 512 --ctx-hi 2304 --heads 32 --kv-heads 8 --dim 128]
     python -m tessel_b200.microbench gemm   [--m 4096 --n 4096 --k 4096] [--kind matmul|linear|gate_up|linear_residual]
     python -m tessel_b200.microbench flash  [--heads 256 --seq 4096 --dim 128]
-    python -m tessel_b200.microbench chunked [--prompt 4096 --chunk 512 --layers 4]
+    python -m tessel_b200.microbench chunked [--prompt 4096 --chunk 512 --layers 32]
     python -m tessel_b200.microbench flash --packed [--prompts 8 --seq 4096 --heads 32 --kv-heads 8 --dim 128]
 
 Each prints one JSON line: the mean device time per launch (CUDA events on the launching
@@ -171,7 +171,7 @@ def flash_packed(gpu, torch, prompts=8, seq=4096, heads=32, kv_heads=32, dim=128
             "peak_tflops": tf, "frac_tensor": flops / (mean * 1e-3) / 1e12 / tf, "peak_kind": kindp}
 
 
-def chunked(gpu, torch, prompt=4096, chunk=512, layers=4, seed=0):
+def chunked(gpu, torch, prompt=4096, chunk=512, layers=32, seed=0):
     """Prefill of one `prompt`-token prompt on a `layers`-layer Llama-3-8B-shaped model: in one
     step, and fed `chunk` tokens at a time through the mixed steps (chunk_attention over the paged
     cache). Wall-clock tokens/s of each, after a warm-up run of the same thing."""
@@ -222,7 +222,7 @@ def main():
     f.add_argument("--prompts", type=int, default=8)
     f.add_argument("--kv-heads", type=int, default=0)
     ck = sub.add_parser("chunked")
-    for name, default in (("prompt", 4096), ("chunk", 512), ("layers", 4)):
+    for name, default in (("prompt", 4096), ("chunk", 512), ("layers", 32)):
         ck.add_argument("--" + name, type=int, default=default)
     a = ap.parse_args()
     import torch

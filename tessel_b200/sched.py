@@ -209,12 +209,12 @@ class Scheduler:
         toks = [s.last for s in run]
         pos = [s.len for s in run]
         slots = [s.pages[s.len // p] * p + s.len % p for s in run]
-        tables = [s.pages for s in run]
         lens = [s.len + 1 for s in run]
         want = list(range(len(run)))
         budget = e.lim.max_tokens - len(run)
         fed = []  # (sequence, tokens fed, row of its last prompt token or -1)
         chunks = []  # (first row, rows, first position) of each piece, for the chunk attention
+        first_rows = []  # (row, pages) of each piece's first row: the only row whose table is read
         for s in self.feeding:
             c = min(self.chunk, s.todo, budget)
             if c <= 0:
@@ -222,17 +222,24 @@ class Scheduler:
             budget -= c
             pr = reqs[s.id].prompt
             chunks.append((len(toks), c, s.len))
-            for i in range(s.len, s.len + c):
-                toks.append(pr[i])
-                pos.append(i)
-                slots.append(s.pages[i // p] * p + i % p)
-                tables.append(s.pages)
-                lens.append(i + 1)
+            first_rows.append((len(toks), s.pages))
+            i = np.arange(s.len, s.len + c)
+            toks.extend(pr[s.len:s.len + c])
+            pos.extend(i.tolist())
+            slots.extend((np.asarray(s.pages, np.int64)[i // p] * p + i % p).tolist())
+            lens.extend((i + 1).tolist())
             last = -1
             if c == s.todo:
                 last = len(toks) - 1
                 want.append(last)
             fed.append((s, c, last))
+        # One padded table for the step: a decode row carries its sequence's pages, a piece's
+        # first row the piece's; the other rows of a piece are never looked up.
+        owners = [(b, s.pages) for b, s in enumerate(run)] + first_rows
+        width = max([len(pg) for _, pg in owners] + [1])
+        tables = np.zeros((len(toks), width), np.int32)
+        for row, pg in owners:
+            tables[row, :len(pg)] = pg
         picks = self._choose(Mixed(tables, lens, chunks), toks, pos, slots, want)
         if run:
             self.absorb(picks[:len(run)])
