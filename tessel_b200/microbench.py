@@ -3,6 +3,7 @@
     python -m tessel_b200.microbench decode [--seqs 256 --ctx-lo 512 --ctx-hi 2304 --heads 32 --kv-heads 8 --dim 128]
     python -m tessel_b200.microbench gemm   [--m 4096 --n 4096 --k 4096] [--kind matmul|linear|gate_up|linear_residual]
     python -m tessel_b200.microbench flash  [--heads 256 --seq 4096 --dim 128]
+    python -m tessel_b200.microbench qkv    [--m 256 --k 4096 --heads 32 --kv-heads 8 --dim 128]
     python -m tessel_b200.microbench chunked [--prompt 4096 --chunk 512 --layers 32]
     python -m tessel_b200.microbench flash --packed [--prompts 8 --seq 4096 --heads 32 --kv-heads 8 --dim 128]
 
@@ -171,6 +172,41 @@ def flash_packed(gpu, torch, prompts=8, seq=4096, heads=32, kv_heads=32, dim=128
             "peak_tflops": tf, "frac_tensor": flops / (mean * 1e-3) / 1e12 / tf, "peak_kind": kindp}
 
 
+def qkv_rope(gpu, torch, m=256, k=4096, heads=32, kv_heads=8, dim=128, iters=20, seed=0):
+    """The QKV projection with rope_q and kv_write as its epilogue (`linear_rope_kv`) at a decode
+    shape, tile chosen by `tb200_tune` unless TB200_GEMM_PLAN forces one; beside it the two-kernel
+    form (`linear` + `rope_kv`) on the same inputs."""
+    from .gpu import Buf
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    npos, ns = 2304, 4096
+    wd = (heads + 2 * kv_heads) * dim
+    x = torch.empty((m, k), dtype=torch.float16, device="cuda").normal_(generator=gen)
+    w = torch.empty((wd, k), dtype=torch.float16, device="cuda").normal_(0, 0.02, generator=gen)
+    pos = (torch.arange(m, dtype=torch.int32, device="cuda") * 7) % npos
+    slot = torch.randperm(ns, device="cuda")[:m].to(torch.int32)
+    c, s_ = torch.rand((npos, dim // 2), device="cuda"), torch.rand((npos, dim // 2), device="cuda")
+    h = lambda *shape: torch.zeros(shape, dtype=torch.float16, device="cuda")
+    qkv, q, kc, vc, kd, vd = h(m, wd), h(m, heads, dim), h(ns, kv_heads, dim), h(ns, kv_heads, dim), \
+        h(m, kv_heads, dim), h(m, kv_heads, dim)
+    buf = lambda t: Buf(t.data_ptr(), t.numel() * t.element_size())
+    fused = [x, w, pos, slot, c, s_, qkv, q, kc, vc, kd, vd]
+    kf = gpu.kernel("linear_rope_kv", [list(a.shape) for a in fused])
+    kl = gpu.kernel("linear", [[m, k], [wd, k], [m, wd]])
+    rope = [qkv, pos, slot, c, s_, q, kc, vc, kd, vd]
+    kr = gpu.kernel("rope_kv", [list(a.shape) for a in rope])
+    fa, la, ra = [buf(a) for a in fused], [buf(x), buf(w), buf(qkv)], [buf(a) for a in rope]
+    plan_f, _ = gpu.tune(kf, fa)
+    plan_l, _ = gpu.tune(kl, la)
+    t = Timer(gpu, torch)
+    f_ms, _ = t.run(lambda: gpu.launch(kf, fa), iters)
+    l_ms, _ = t.run(lambda: gpu.launch(kl, la), iters)
+    r_ms, _ = t.run(lambda: gpu.launch(kr, ra), iters)
+    return {"kernel": "linear_rope_kv", "m": m, "k": k, "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
+            "fused_us": f_ms * 1e3, "fused_plan": list(plan_f), "linear_us": l_ms * 1e3, "linear_plan": list(plan_l),
+            "rope_kv_us": r_ms * 1e3}
+
+
 def chunked(gpu, torch, prompt=4096, chunk=512, layers=32, seed=0):
     """Prefill of one `prompt`-token prompt on a `layers`-layer Llama-3-8B-shaped model: in one
     step, and fed `chunk` tokens at a time through the mixed steps (chunk_attention over the paged
@@ -221,6 +257,9 @@ def main():
                    help="the packed prefill form: --prompts prompts of --seq tokens, --heads query heads on --kv-heads")
     f.add_argument("--prompts", type=int, default=8)
     f.add_argument("--kv-heads", type=int, default=0)
+    qk = sub.add_parser("qkv")
+    for name, default in (("m", 256), ("k", 4096), ("heads", 32), ("kv-heads", 8), ("dim", 128), ("iters", 20)):
+        qk.add_argument("--" + name, type=int, default=default)
     ck = sub.add_parser("chunked")
     for name, default in (("prompt", 4096), ("chunk", 512), ("layers", 32)):
         ck.add_argument("--" + name, type=int, default=default)
@@ -234,6 +273,8 @@ def main():
         r = decode(gpu, torch, a.seqs, a.ctx_lo, a.ctx_hi, a.heads, a.kv_heads, a.dim, a.iters)
     elif a.cmd == "gemm":
         r = gemm(gpu, torch, a.m, a.n, a.k, a.kind, a.iters)
+    elif a.cmd == "qkv":
+        r = qkv_rope(gpu, torch, a.m, a.k, a.heads, a.kv_heads, a.dim, a.iters)
     elif a.cmd == "chunked":
         r = chunked(gpu, torch, a.prompt, a.chunk, a.layers)
     elif a.packed:
