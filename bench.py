@@ -68,6 +68,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-micro", action="store_true", help="skip the single-kernel numbers (N = 1)")
     ap.add_argument("--profile-steps", type=int, default=2)
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the device-resident timed region with cudaProfilerStart/Stop "
+                         "(for `ncu --profile-from-start off`)")
     ap.add_argument("--tp-exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: cross-rank sums by the fused peer-memory kernel, or by NCCL allreduce")
     return ap.parse_args()
@@ -436,7 +439,11 @@ def run_ours(args, wl):
         config["l2"] = "inputs larger than L2 (weights + KV read per step: %.1f GB per GPU)" % ((wbytes + kvbytes) / 1e9)
     launches0 = gpu.kernel_launches()
     launches_before = launches0  # kernels launched before the device-resident timed region (a profiler's skip count)
+    if args.profiler_range:
+        torch.cuda.cudart().cudaProfilerStart()
     dev_ms = resident(K)
+    if args.profiler_range:
+        torch.cuda.cudart().cudaProfilerStop()
     clock_rec = clocks.stop()
     dev_launches = gpu.kernel_launches() - launches0
     ctx_mid = config["mean_context"]

@@ -3,6 +3,7 @@
     python -m tessel_b200.microbench decode [--seqs 256 --ctx-lo 512 --ctx-hi 2304 --heads 32 --kv-heads 8 --dim 128]
     python -m tessel_b200.microbench gemm   [--m 4096 --n 4096 --k 4096] [--kind matmul|linear|gate_up|linear_residual]
     python -m tessel_b200.microbench flash  [--heads 256 --seq 4096 --dim 128]
+    python -m torch.distributed.run --nproc-per-node N -m tessel_b200.microbench exchange [--k-cols 4096]
     python -m tessel_b200.microbench qkv    [--m 256 --k 4096 --heads 32 --kv-heads 8 --dim 128]
     python -m tessel_b200.microbench chunked [--prompt 4096 --chunk 512 --layers 32]
     python -m tessel_b200.microbench flash --packed [--prompts 8 --seq 4096 --heads 32 --kv-heads 8 --dim 128]
@@ -207,6 +208,99 @@ def qkv_rope(gpu, torch, m=256, k=4096, heads=32, kv_heads=8, dim=128, iters=20,
             "rope_kv_us": r_ms * 1e3}
 
 
+def exchange(torch, tokens=256, dim=4096, k_cols=4096, calls=64, reps=10):
+    """Per-call device time of the tensor-parallel exchange, replayed as a graph of `calls`
+    projection + exchange pairs (what a decode step does `2 x layers` times): the peer-memory
+    form (`linear_scatter` + `tp_reduce_norm`) and the NCCL form (`linear_f32` + allreduce +
+    `residual_add` + `rmsnorm`), each rank projecting `k_cols / N` input columns onto `dim`
+    outputs. Launch under torchrun, one rank per GPU; rank 0 returns the result, the others None."""
+    import torch.distributed as dist
+    from .gpu import Buf, F32, Gpu, I32
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    gpu = Gpu(local)
+    ids = [gpu.comm_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    gpu.comm_init(rank, world, ids[0])
+    T, kl = tokens, k_cols // world
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1 + rank)
+    xin = torch.empty((T, kl), dtype=torch.float16, device="cuda").normal_(generator=gen)
+    wt = torch.empty((dim, kl), dtype=torch.float16, device="cuda").normal_(0, 0.02, generator=gen)
+    gain = torch.ones((dim,), dtype=torch.float16, device="cuda")
+    tbuf = lambda t: Buf(t.data_ptr(), t.numel() * t.element_size())
+    _, fb, eb = gpu.tp_sizes()
+    a = gpu.alloc
+    mine = [a((T + world) * dim * 4), a((T + world) * dim * 4), a(T * dim * 4), a(T * dim * 2), a(T * dim * 8), a(fb)]
+    everyone = [None] * world
+    dist.all_gather_object(everyone, [gpu.ipc_export(b) for b in mine])
+    cols = [[b if r == rank else gpu.ipc_import(everyone[r][i], b.bytes) for r in range(world)]
+            for i, b in enumerate(mine)]
+    raw = gpu.tp_table(rank, world, cols[0], cols[1], cols[2], cols[3], cols[4], cols[5], a(eb))
+    table = gpu.tensor(np.frombuffer(raw, np.uint8).copy())
+    x, h = mine[2], mine[3]
+    part = a(T * dim * 4)
+    ks = gpu.kernel("linear_scatter", [[T, kl], [dim, kl], [table.bytes]])
+    kt = gpu.kernel("tp_reduce_norm", [[table.bytes], [dim], [T, dim]])
+    kf = gpu.kernel("linear_f32", [[T, kl], [dim, kl], [T, dim]])
+    kr = gpu.kernel("residual_add", [[T, dim], [T, dim]])
+    kn = gpu.kernel("rmsnorm", [[T, dim], [dim], [T, dim]])
+    gpu.tune(ks, [tbuf(xin), tbuf(wt), table, I32(0)])
+    gpu.tune(kf, [tbuf(xin), tbuf(wt), part])
+    eps = F32(1e-5)
+
+    def peer(n):
+        for i in range(n):
+            gpu.launch(ks, [tbuf(xin), tbuf(wt), table, I32(i & 1)])
+            gpu.launch(kt, [table, tbuf(gain), x, eps, I32(i & 1), I32(1), I32(world)])
+
+    def nccl(n):
+        for _ in range(n):
+            gpu.launch(kf, [tbuf(xin), tbuf(wt), part])
+            gpu.allreduce(part, T * dim, 0)
+            gpu.launch(kr, [x, part])
+            gpu.launch(kn, [x, tbuf(gain), h, eps])
+
+    out = {"kernel": "tp_exchange", "ranks": world, "tokens": T, "dim": dim, "k_per_rank": kl, "calls_per_graph": calls}
+    for name, fn in (("peer_memory", peer), ("nccl", nccl)):
+        fn(4)
+        gpu.sync()
+        dist.barrier()
+        gpu.capture_begin()
+        fn(calls)
+        g = gpu.capture_end()
+        for _ in range(3):
+            gpu.replay(g)
+        gpu.sync()
+        dist.barrier()
+        gpu.time_begin()
+        for _ in range(reps):
+            gpu.replay(g)
+        ms = gpu.time_end()
+        gpu.sync()
+        t = torch.tensor([ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out[name + "_us_per_pair"] = float(t[0]) / (reps * calls) * 1e3
+    # The projection alone, for the difference.
+    gpu.capture_begin()
+    for _ in range(calls):
+        gpu.launch(kf, [tbuf(xin), tbuf(wt), part])
+    g = gpu.capture_end()
+    gpu.replay(g)
+    gpu.sync()
+    gpu.time_begin()
+    for _ in range(reps):
+        gpu.replay(g)
+    out["linear_f32_alone_us"] = gpu.time_end() / (reps * calls) * 1e3
+    gpu.sync()
+    dist.barrier()
+    dist.destroy_process_group()
+    return out if rank == 0 else None
+
+
 def chunked(gpu, torch, prompt=4096, chunk=512, layers=32, seed=0):
     """Prefill of one `prompt`-token prompt on a `layers`-layer Llama-3-8B-shaped model: in one
     step, and fed `chunk` tokens at a time through the mixed steps (chunk_attention over the paged
@@ -257,6 +351,9 @@ def main():
                    help="the packed prefill form: --prompts prompts of --seq tokens, --heads query heads on --kv-heads")
     f.add_argument("--prompts", type=int, default=8)
     f.add_argument("--kv-heads", type=int, default=0)
+    ex = sub.add_parser("exchange", help="under torchrun: python -m torch.distributed.run --nproc-per-node N -m tessel_b200.microbench exchange")
+    for name, default in (("tokens", 256), ("dim", 4096), ("k-cols", 4096), ("calls", 64)):
+        ex.add_argument("--" + name, type=int, default=default)
     qk = sub.add_parser("qkv")
     for name, default in (("m", 256), ("k", 4096), ("heads", 32), ("kv-heads", 8), ("dim", 128), ("iters", 20)):
         qk.add_argument("--" + name, type=int, default=default)
@@ -267,6 +364,11 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a B200: there is no CPU path")
+    if a.cmd == "exchange":
+        r = exchange(torch, a.tokens, a.dim, a.k_cols, a.calls)
+        if r is not None:
+            print(json.dumps(r), flush=True)
+        return
     from .gpu import Gpu
     gpu = Gpu(0)
     if a.cmd == "decode":
