@@ -428,7 +428,12 @@ int make_decode(Ctx* c, Op& op) {
   const int hgroups = (d.H / d.G + 7) / 8;
   const long long units = (long long)d.B * d.G * hgroups;
   long long want = (4LL * c->sm_count + units - 1) / units;
-  if (const char* e = getenv("TB200_DECODE_SPLITS")) want = atoi(e);  // tuning and tests
+  if (const char* e = getenv("TB200_DECODE_SPLITS")) {  // tuning and tests; a value that is not a count is an error
+    char* end = nullptr;
+    const long v = strtol(e, &end, 10);
+    if (end == e || *end != 0 || v < 1 || v > 4096) return bad("TB200_DECODE_SPLITS must be a positive integer");
+    want = v;
+  }
   int max_split = (d.MP + 3) / 4;
   // Once every SM has a CTA or two anyway, more splits only shorten the tail, and a split costs
   // its start-up (barriers, the first pages' latency) and a partial to merge: measured at 256
