@@ -127,7 +127,8 @@ int tb200_launch(tb200_ctx* ctx, tb200_op op, const uint64_t* args, int n_args);
  * every later launch of `op`. `plan`, if not NULL, receives the choice as
  * {MT, BN, splits} (MT 3 = a CTA pair; zeros for a kernel with nothing to
  * choose), `best_us` its median time. Other kernels: nothing to tune, success.
- * Not during capture; allocates and frees a 192 MB scratch buffer. With
+ * Not during capture; allocates and frees a 192 MB scratch buffer (timing goes
+ * on without the L2 overwrite if that allocation fails). With
  * TB200_GEMM_PLAN set in the environment the forced plan stays. */
 int tb200_tune(tb200_ctx* ctx, tb200_op op, const uint64_t* args, int n_args, int32_t* plan, float* best_us);
 

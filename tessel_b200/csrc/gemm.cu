@@ -1214,7 +1214,11 @@ int tune_gemm(Ctx* c, Op& op, const uint64_t* a, float* best_us) {
   if (cands.size() > 8) cands.resize(8);
   const size_t flush_bytes = (size_t)192 << 20;
   void* flush = nullptr;
-  TB_CUDA(c, cudaMalloc(&flush, flush_bytes));
+  if (cudaMalloc(&flush, flush_bytes) != cudaSuccess) {
+    // No room for the buffer that overwrites the L2: time the candidates without it rather than fail.
+    cudaGetLastError();
+    flush = nullptr;
+  }
   cudaEvent_t e0 = nullptr, e1 = nullptr;
   cudaEventCreate(&e0);
   cudaEventCreate(&e1);
@@ -1227,7 +1231,7 @@ int tune_gemm(Ctx* c, Op& op, const uint64_t* a, float* best_us) {
     float times[ITERS];
     bool ok = true;
     for (int it = 0; it < WARM + ITERS && ok; ++it) {
-      ok = cudaMemsetAsync(flush, it, flush_bytes, c->stream) == cudaSuccess;
+      ok = flush == nullptr || cudaMemsetAsync(flush, it, flush_bytes, c->stream) == cudaSuccess;
       ok = ok && cudaEventRecord(e0, c->stream) == cudaSuccess;
       ok = ok && launch_plan(c, op, a, pl.mt, pl.bn, pl.splits) == 0;
       ok = ok && cudaEventRecord(e1, c->stream) == cudaSuccess;
@@ -1251,7 +1255,7 @@ int tune_gemm(Ctx* c, Op& op, const uint64_t* a, float* best_us) {
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   cudaStreamSynchronize(c->stream);
-  cudaFree(flush);
+  if (flush) cudaFree(flush);
   if (rc) return rc;
   op.p1 = pick.mt;
   op.p2 = pick.bn;

@@ -150,6 +150,8 @@ __global__ void __launch_bounds__(FA_THREADS, 1)
   if (p.paged) {
     const int* m = p.meta + 4 * blockIdx.z;
     const int row0 = m[0], nrows = m[1], pos0 = m[2];
+    // A descriptor that does not lie inside the step is skipped, not trusted.
+    if (row0 < 0 || nrows <= 0 || pos0 < 0 || row0 + nrows > p.S) return;
     if (i0 >= nrows) return;  // uniform for the CTA, before any barrier or tensor memory exists
     qrow0 = row0 + i0, rpos0 = pos0 + i0, slim = pos0 + nrows, trow = row0;
   }
@@ -509,6 +511,7 @@ __global__ void chunk_generic_kernel(const __half* __restrict__ Q, const __half*
   const int lane = threadIdx.x & 31;
   const int* m = meta + 4 * blockIdx.y;
   const int row0 = m[0], nrows = m[1], pos0 = m[2];
+  if (row0 < 0 || nrows <= 0 || pos0 < 0 || row0 + nrows > T) return;  // a descriptor outside the step is skipped
   const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (w >= (long long)nrows * H) return;
   const int r = (int)(w / H), h = (int)(w % H), g = h / (H / G);
