@@ -3,7 +3,8 @@
 Host-side mirror of tessel's ``src/llm/safetensors.rs``: ``config`` (:189-226),
 the tensor index over ``model.safetensors`` or the files named by
 ``model.safetensors.index.json`` (:236-292), dtype conversion to f16 (F16 as is,
-BF16 and F32 rounded to nearest even, :295-321), ``load`` (:324-367) and ``save``
+BF16 and F32 rounded to nearest even, :295-321; beyond the reference, F8_E4M3 with its scale
+tensor is dequantised), ``load`` (:324-367) and ``save``
 (:369-443). Unlike the reference, ``load`` can return one tensor-parallel rank's
 shard directly: files are memory-mapped and only the rows (wqkv, wg, wu) or
 columns (wo, wd) that the rank keeps are read and converted, so eight ranks
@@ -72,7 +73,7 @@ class _Entry:
     end: int
 
 
-_DTYPES = {"F16": (np.float16, 2), "BF16": (np.uint16, 2), "F32": (np.float32, 4)}
+_DTYPES = {"F16": (np.float16, 2), "BF16": (np.uint16, 2), "F32": (np.float32, 4), "F8_E4M3": (np.uint8, 1)}
 
 
 class Index:
@@ -153,13 +154,28 @@ class Index:
         """Rows ``rows`` and columns ``cols`` of the tensor as f16 (BF16 and F32 rounded to
         nearest even), in memory of its own."""
         a = self.raw(name, shape)
-        bf16 = self.entries[name].dtype == "BF16"
+        dtype = self.entries[name].dtype
         if rows is not None:
             a = a[rows]
         if cols is not None:
             a = a[:, cols]
-        if bf16:
+        if dtype == "BF16":
             a = (a.astype(np.uint32) << 16).view(np.float32)
+        elif dtype == "F8_E4M3":
+            # E4M3 bytes, with the scale tensor FP8 checkpoints store beside a weight
+            # ("....weight_scale": one f32 for the tensor, or one per output row).
+            from . import fp8
+            a = fp8.decode(a)
+            sname = name + "_scale"
+            if sname in self.entries:
+                e = self.entries[sname]
+                sc = self.raw(sname, e.shape).astype(np.float32).reshape(-1)
+                if sc.size == 1:
+                    a = a * sc[0]
+                elif sc.size == shape[0]:
+                    a = a * (sc[rows] if rows is not None else sc)[:, None]
+                else:
+                    raise CheckpointError(f"{sname}: {sc.size} scales for a tensor of {shape[0]} rows")
         with np.errstate(over="ignore"):
             return np.ascontiguousarray(a.astype(np.float16))
 
@@ -206,7 +222,8 @@ def save(w: Weights, path: str, dtype: str = "F16") -> None:
     """Writes ``w`` (a whole model) as a checkpoint directory laid out as Hugging Face lays out a
     Llama model: ``config.json`` and one ``model.safetensors``. ``dtype`` "F16" (what the
     reference writes), "BF16" or "F32" choose the stored type (the latter two for tests of the
-    conversions)."""
+    conversions); "F8_E4M3" stores the projection matrices as E4M3 bytes with one f32 scale per
+    output row in "<name>_scale" (tessel_b200/fp8.py) and everything else as F16."""
     if dtype not in _DTYPES:
         raise CheckpointError(f"dtype {dtype} not supported")
     c = w.cfg
@@ -241,15 +258,26 @@ def save(w: Weights, path: str, dtype: str = "F16") -> None:
             return a.astype(np.float32)
         return (a.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)  # truncated to bf16's 8 significant bits
 
-    head, off = {}, 0
+    blobs: List[Tuple[str, str, tuple, bytes]] = []  # name, dtype, shape, bytes
     for name, a in tensors:
-        n = int(np.prod(a.shape)) * _DTYPES[dtype][1]
-        head[name] = {"dtype": dtype, "shape": list(a.shape), "data_offsets": [off, off + n]}
-        off += n
+        if dtype == "F8_E4M3":
+            if "_proj.weight" in name:
+                from . import fp8
+                q, sc = fp8.quantize_rows(np.asarray(a, np.float32))
+                blobs.append((name, "F8_E4M3", a.shape, q.tobytes()))
+                blobs.append((name + "_scale", "F32", sc.shape, sc.tobytes()))
+            else:
+                blobs.append((name, "F16", a.shape, np.ascontiguousarray(a, np.float16).tobytes()))
+        else:
+            blobs.append((name, dtype, a.shape, stored(a).tobytes()))
+    head, off = {}, 0
+    for name, dt, shape, raw in blobs:
+        head[name] = {"dtype": dt, "shape": list(shape), "data_offsets": [off, off + len(raw)]}
+        off += len(raw)
     hb = json.dumps(head).encode("utf-8")
     hb += b" " * (-len(hb) % 8)
     with open(os.path.join(path, "model.safetensors"), "wb") as fh:
         fh.write(struct.pack("<Q", len(hb)))
         fh.write(hb)
-        for _, a in tensors:
-            fh.write(stored(a).tobytes())
+        for _, _, _, raw in blobs:
+            fh.write(raw)

@@ -46,6 +46,12 @@ enum Kind : int {
   K_CHUNK_ATTENTION,  // causal attention of a prompt chunk's rows against the paged cache
   K_LINEAR_SCATTER,   // a tensor-parallel rank's partial product, each row stored into its owner rank's memory
   K_LINEAR_ROPE_KV,   // the QKV projection with rope_q and kv_write as its epilogue
+  // FP8 mode (non-parity): E4M3 operands with one f32 scale per row, f32 accumulation.
+  K_QUANT_ROWS,          // X f16 [M,K] -> Q u8 [M,K], S f32 [M]
+  K_RMSNORM_Q8,          // RMSNorm followed by quant_rows of its f16 result
+  K_LINEAR_Q8,           // Y f16 = (Xq sx) (Wq sw)^T
+  K_LINEAR_RESIDUAL_Q8,  // R f32 += (Xq sx) (Wq sw)^T
+  K_GATE_UP_Q8,          // Y f16 = silu((Xq sx)(Wgq sg)^T) * ((Xq sx)(Wuq su)^T)
   K_COUNT
 };
 
@@ -82,6 +88,8 @@ struct Op {
   // A scalar launch argument on its way into the kernel's parameters (linear_scatter: which inbox).
   int aux = 0;
   RopeArgs rope;
+  // FP8 kinds: a launch's scale arrays (rows of X, rows of W, rows of Wu) on their way to the kernel.
+  const float* q8[3] = {nullptr, nullptr, nullptr};
   std::vector<MapEntry> maps;
 
   // The cached maps for `key`, or null; `fresh` returns a slot to fill (the cache is emptied
@@ -394,6 +402,17 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, u
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The same on E4M3 operands (kind::f8f6f4: 32 bytes of K per instruction, where f16 has 16
+// elements; the instruction descriptor's format fields are 0 for E4M3 as they are for f16).
+__device__ __forceinline__ void umma_q8_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }

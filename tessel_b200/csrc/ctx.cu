@@ -89,6 +89,11 @@ static const KindInfo KINDS[] = {
     {"chunk_attention", K_CHUNK_ATTENTION, 6, 7},
     {"linear_scatter", K_LINEAR_SCATTER, 3, 4},
     {"linear_rope_kv", K_LINEAR_ROPE_KV, 12, 12},
+    {"quant_rows", K_QUANT_ROWS, 3, 3},
+    {"rmsnorm_q8", K_RMSNORM_Q8, 4, 5},
+    {"linear_q8", K_LINEAR_Q8, 5, 5},
+    {"linear_residual_q8", K_LINEAR_RESIDUAL_Q8, 5, 5},
+    {"gate_up_q8", K_GATE_UP_Q8, 7, 7},
 };
 
 static std::string shape_text(const std::vector<int64_t>& s) {
@@ -113,7 +118,8 @@ static int profile_add(Ctx* c, const std::string& kernel) {
 
 static bool is_gemm(Kind k) {
   return k == K_LINEAR || k == K_LINEAR_RESIDUAL || k == K_LOGITS || k == K_GATE_UP || k == K_MATMUL ||
-         k == K_LINEAR_F32 || k == K_LINEAR_SCATTER || k == K_LINEAR_ROPE_KV;
+         k == K_LINEAR_F32 || k == K_LINEAR_SCATTER || k == K_LINEAR_ROPE_KV || k == K_LINEAR_Q8 ||
+         k == K_LINEAR_RESIDUAL_Q8 || k == K_GATE_UP_Q8;
 }
 
 }  // namespace tb

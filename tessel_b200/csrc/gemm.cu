@@ -6,6 +6,8 @@
 //   matmul           C f16 = A B, B [K,N] row-major    kernels/matmul.tl:3-17
 //   linear_f32       Y f32 = X W^T (a tensor-parallel partial; no counterpart)
 //   linear_scatter   linear_f32 whose rows go to their owner ranks' memory (no counterpart)
+//   linear_q8, linear_residual_q8, gate_up_q8   the same three with E4M3 operands and per-row
+//                    f32 scales (tcgen05 kind::f8f6f4, f32 accumulation; a non-parity mode)
 //   linear_rope_kv   the QKV projection with rope_q and kv_write (kernels/llm.tl:78-112) as its
 //                    epilogue: the rounded product is rotated and scattered into Q, the dense K and
 //                    V and the cache pages straight from the accumulators (no counterpart as one
@@ -71,6 +73,8 @@ struct GemmParams {
   int M, N, K, splits;
   unsigned int* status;
   RopeArgs rope;
+  // FP8 mode: f32 scales of the E4M3 operands, one per row of X and per row of W (and of Wu).
+  const float *sa, *sb, *sb2;
   // linear_scatter: row r goes to rank r % n's inbox `which`, at [this rank][r / n]; null otherwise.
   const TpTable* scatter;
   int which;
@@ -272,6 +276,14 @@ __device__ __forceinline__ void rope_store(const GemmParams& p, int row, int gc,
   }
 }
 
+// FP8 mode: 32 accumulator columns of one row back to real units: x (row scale of X) x (row
+// scale of W, one per output column).
+__device__ __forceinline__ void q8_scale(const GemmParams& p, const float* sb, int row, int col0, float* v) {
+  const float sa = row < p.M ? p.sa[row] : 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] *= sa * (col0 + j < p.N ? sb[col0 + j] : 0.f);
+}
+
 // The epilogue of one CTA: warps 2-9 read the CTA's MT x 128 rows of the finished accumulators
 // out of tensor memory (TMEM lane quadrant = warp % 4, one output row per thread; the two warps
 // of a quadrant share the 32-column units between them) and store them. With S > 1 the S CTAs
@@ -281,7 +293,7 @@ __device__ __forceinline__ void rope_store(const GemmParams& p, int row, int gc,
 // into the ring (idle by then) of the unit's owner, and the owner adds the partials in split
 // order. `split` is this CTA's index among the S; the CTA holding split s of the same tile has
 // cluster rank s * rank_stride + rank_off.
-template <int MT, int BN, int NB, int EPI>
+template <int MT, int BN, int NB, int EPI, bool Q8 = false>
 __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem, unsigned char* smem,
                                               uint64_t* acc_full, int m0, int n0, int S, uint32_t split,
                                               uint32_t rank_stride, uint32_t rank_off, int ring_bytes) {
@@ -403,12 +415,23 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem
           uint32_t r2[32];
           tmem_ld32(tmem + lane_base + mt * NB + BN + c0, r2);
           tmem_ld_wait();
+          if (Q8) {
+            float u[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j]));
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]), u[j] = __uint_as_float(r2[j]);
+            q8_scale(p, p.sb, row, n0 + c0, v);
+            q8_scale(p, p.sb2, row, n0 + c0, u);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu_mul(v[j], u[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r2[j]));
+          }
         } else {
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (Q8) q8_scale(p, p.sb, row, n0 + c0, v);
         }
         if (scatter)
           scatter_store(p, turn, row, n0 + c0, v);
@@ -423,6 +446,7 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, uint32_t tmem
       const int u = gi;  // groups are single units here
       float v[32];
       sum_unit(u, v);
+      if (Q8) q8_scale(p, p.sb, m0 + (u / CH) * BM + rit, n0 + (u % CH) * 32, v);
       if (scatter)
         scatter_store(p, turn, m0 + (u / CH) * BM + rit, n0 + (u % CH) * 32, v);
       else
@@ -572,7 +596,7 @@ struct PairCfg {
 
 // Grid: (2 x row pairs, column tiles, K splits), cluster (2, 1, splits): cluster rank =
 // (blockIdx.x & 1) + 2 * split. K-major weights only (W [N, K]).
-template <int BN, int EPI>
+template <int BN, int EPI, bool Q8 = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                      const __grid_constant__ CUtensorMap mapB2, const GemmParams p) {
@@ -590,7 +614,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
   const uint32_t half = crank & 1u;        // which 128 rows of the pair's 256
   const uint32_t leader = crank & ~1u;     // cluster rank of the pair's even CTA
   const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
-  const int nk = (p.K + BK - 1) / BK;
+  // A stage holds 128 bytes of K per row either way: 64 halves, or (FP8 mode) 128 E4M3 bytes.
+  constexpr int BKE = Q8 ? 2 * BK : BK;
+  const int nk = (p.K + BKE - 1) / BKE;
   const int S = p.splits;
   const int k_begin = (int)((long long)nk * blockIdx.z / S), k_end = (int)((long long)nk * (blockIdx.z + 1) / S);
   const int niter = k_end - k_begin;
@@ -624,7 +650,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       // As in gemm_kernel: weight tiles are requested before waiting for the previous kernel.
       const int pre = niter < STAGES ? niter : STAGES;
       auto load_b = [&](int i) {
-        const int s = i % STAGES, kc = (k_begin + i) * BK;
+        const int s = i % STAGES, kc = (k_begin + i) * BKE;
         unsigned char* b = smem + s * Cfg::STAGE + Cfg::A_BYTES;
         const uint32_t bar = cluster_map(smem_u32(&full[s]), leader);
         if (half == 0) mbar_expect_tx(&full[s], 2 * Cfg::STAGE);  // this CTA's tiles and the partner's
@@ -634,7 +660,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
       for (int i = 0; i < pre; ++i) load_b(i);
       pdl_wait();
       for (int i = 0; i < niter; ++i) {
-        const int s = i % STAGES, k = i / STAGES, kc = (k_begin + i) * BK;
+        const int s = i % STAGES, k = i / STAGES, kc = (k_begin + i) * BKE;
         if (i >= pre) {
           mbar_wait(&empty[s], (k & 1) ^ 1, p.status, 211);
           load_b(i);
@@ -657,9 +683,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         for (int kk = 0; kk < BK / 16; ++kk) {
           const uint64_t ad = umma_desc_sw128(a + kk * 32, 16, 1024);
 #pragma unroll
-          for (int op = 0; op < Cfg::NOPS; ++op)
-            umma_f16_pair(tmem + op * BN, ad, umma_desc_sw128(b + op * (NBH * BK * 2) + kk * 32, 16, 1024), idesc,
-                          (i > 0 || kk > 0) ? 1u : 0u);
+          for (int op = 0; op < Cfg::NOPS; ++op) {
+            const uint64_t bd = umma_desc_sw128(b + op * (NBH * BK * 2) + kk * 32, 16, 1024);
+            if (Q8)
+              umma_q8_pair(tmem + op * BN, ad, bd, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            else
+              umma_f16_pair(tmem + op * BN, ad, bd, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         umma_commit_pair(&empty[s], both);  // frees the slot in both CTAs once these MMAs have read it
       }
@@ -668,7 +698,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
   }
   __syncwarp();
-  tile_epilogue<1, BN, Cfg::NB, EPI>(p, tmem, smem, acc_full, m0, n0, S, crank >> 1, 2u, half, Cfg::BAR_OFF);
+  tile_epilogue<1, BN, Cfg::NB, EPI, Q8>(p, tmem, smem, acc_full, m0, n0, S, crank >> 1, 2u, half, Cfg::BAR_OFF);
   if (warp == 2 && (threadIdx.x & 31) == 0) TB_TRACE(8);
   // Both CTAs have read their accumulators (and every barrier signal of the pair has landed)
   // before either frees tensor memory or leaves.
@@ -738,6 +768,7 @@ __global__ void gemm_plain_kernel(const __half* __restrict__ A, const __half* __
 struct GemmShape {
   int M, N, K;
   int D = 0;  // linear_rope_kv: head_dim (a tile must hold whole heads)
+  int q8 = 0;  // FP8 kinds: a K slice is 128 elements, CTA pairs only
 };
 
 GemmShape gemm_shape(const Op& op) {
@@ -746,6 +777,11 @@ GemmShape gemm_shape(const Op& op) {
   g.M = (int)s[0][0];
   g.K = (int)s[0][1];
   g.N = op.kind == K_MATMUL ? (int)s[1][1] : (int)s[1][0];
+  // FP8 kinds: Xq[M,K], sx[M], Wq[N,K], sw[N], (Wuq[N,K], su[N],) out[M,N]
+  if (op.kind == K_LINEAR_Q8 || op.kind == K_LINEAR_RESIDUAL_Q8 || op.kind == K_GATE_UP_Q8) {
+    g.N = (int)s[2][0];
+    g.q8 = 1;
+  }
   if (op.kind == K_LINEAR_ROPE_KV) g.D = (int)s[7][2];  // Q[T,H,D]
   return g;  // linear_scatter, linear_rope_kv: X[M,K], W[N,K] lead as in linear
 }
@@ -754,10 +790,13 @@ int epi_of(Kind k) {
   switch (k) {
     case K_LINEAR:
     case K_MATMUL:
+    case K_LINEAR_Q8:
       return EPI_F16;
     case K_LINEAR_RESIDUAL:
+    case K_LINEAR_RESIDUAL_Q8:
       return EPI_RESID;
     case K_GATE_UP:
+    case K_GATE_UP_Q8:
       return EPI_GATE_UP;
     case K_LINEAR_ROPE_KV:
       return EPI_ROPE;
@@ -823,39 +862,44 @@ int run(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, const voi
   p.scatter = op.kind == K_LINEAR_SCATTER ? (const TpTable*)out : nullptr;
   p.which = op.aux;
   p.rope = op.rope;
+  p.sa = p.sb = p.sb2 = nullptr;
   const dim3 grid((g.M + MT * BM - 1) / (MT * BM), (g.N + BN - 1) / BN, splits);
   TB_CUDA(c, launch_k(c, gemm_kernel<MT, BN, EPI, B_MN>, grid, dim3(GEMM_THREADS), Cfg::SMEM, splits, ma, mb, mb2, p));
   return 0;
 }
 
-template <int BN, int EPI>
+template <int BN, int EPI, bool Q8 = false>
 int run_pair(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, const void* B, const void* B2, void* out,
              bool attr_only) {
   using Cfg = PairCfg<BN, EPI>;
   if (attr_only) {
-    TB_CUDA(c, cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+    TB_CUDA(c, cudaFuncSetAttribute(gemm_pair_kernel<BN, EPI, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
     return 0;
   }
   const uint64_t key[4] = {(uint64_t)A, (uint64_t)B, (uint64_t)B2, ((uint64_t)PAIR << 32) | ((uint64_t)BN << 8) | (uint64_t)splits};
+  // Rows of 128 bytes of K either way: 64 halves, or 128 E4M3 bytes.
+  const CUtensorMapDataType dt = Q8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const uint64_t pitch = (uint64_t)g.K * (Q8 ? 1 : 2);
+  const uint32_t bk = Q8 ? 2 * BK : BK;
   const MapEntry* hit = op.find_maps(key);
   if (!hit) {
     CUtensorMap ma, mb, mb2;
     {
       const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.M};
-      const uint64_t strides[1] = {(uint64_t)g.K * 2};
-      const uint32_t box[2] = {BK, BM};
-      if (make_tensor_map(c, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      const uint64_t strides[1] = {pitch};
+      const uint32_t box[2] = {bk, BM};
+      if (make_tensor_map(c, &ma, dt, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
         return 1;
     }
     {
       const uint64_t dims[2] = {(uint64_t)g.K, (uint64_t)g.N};
-      const uint64_t strides[1] = {(uint64_t)g.K * 2};
-      const uint32_t box[2] = {BK, Cfg::NBH};
-      if (make_tensor_map(c, &mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      const uint64_t strides[1] = {pitch};
+      const uint32_t box[2] = {bk, Cfg::NBH};
+      if (make_tensor_map(c, &mb, dt, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
         return 1;
       mb2 = mb;
       if (EPI == EPI_GATE_UP &&
-          make_tensor_map(c, &mb2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, B2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+          make_tensor_map(c, &mb2, dt, 2, B2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
         return 1;
     }
     MapEntry* e = op.fresh_maps(key);
@@ -873,14 +917,25 @@ int run_pair(Ctx* c, Op& op, const GemmShape& g, int splits, const void* A, cons
   p.scatter = op.kind == K_LINEAR_SCATTER ? (const TpTable*)out : nullptr;
   p.which = op.aux;
   p.rope = op.rope;
+  p.sa = op.q8[0], p.sb = op.q8[1], p.sb2 = op.q8[2];
   const dim3 grid(2 * ((g.M + 2 * BM - 1) / (2 * BM)), (g.N + BN - 1) / BN, splits);
-  TB_CUDA(c, launch_kc(c, gemm_pair_kernel<BN, EPI>, grid, dim3(GEMM_THREADS), Cfg::SMEM, 2, splits, ma, mb, mb2, p));
+  TB_CUDA(c, launch_kc(c, gemm_pair_kernel<BN, EPI, Q8>, grid, dim3(GEMM_THREADS), Cfg::SMEM, 2, splits, ma, mb, mb2, p));
   return 0;
 }
+
+bool is_q8(Kind k) { return k == K_LINEAR_Q8 || k == K_LINEAR_RESIDUAL_Q8 || k == K_GATE_UP_Q8; }
 
 template <int BN>
 int dispatch_pair(Ctx* c, Op& op, Kind kind, const GemmShape& g, int splits, const void* A, const void* B, const void* B2,
                   void* out, bool attr_only) {
+  if (is_q8(kind)) {
+    if constexpr (BN == 128 || BN == 256) {
+      if (kind == K_GATE_UP_Q8) return run_pair<BN, EPI_GATE_UP, true>(c, op, g, splits, A, B, B2, out, attr_only);
+      if (kind == K_LINEAR_Q8) return run_pair<BN, EPI_F16, true>(c, op, g, splits, A, B, B2, out, attr_only);
+      return run_pair<BN, EPI_RESID, true>(c, op, g, splits, A, B, B2, out, attr_only);
+    }
+    return fail(c, "gemm: FP8 tiles are 128 or 256 columns wide");
+  }
   switch (epi_of(kind)) {
     case EPI_GATE_UP:
       return run_pair<BN, EPI_GATE_UP>(c, op, g, splits, A, B, B2, out, attr_only);
@@ -956,7 +1011,9 @@ struct Plan {
 // partial tiles must fit the ring they are received in.
 const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
   const int epi = epi_of(kind);
-  const int nk = (g.K + BK - 1) / BK;
+  const int bke = g.q8 ? 2 * BK : BK;
+  const int nk = (g.K + bke - 1) / bke;
+  if (g.q8 && (mt != PAIR || (bn != 128 && bn != 256))) return "FP8 projections run on CTA pairs of 128 or 256 columns";
   // Units of the tile that one CTA must own together, and how many such groups a tile has.
   const int uh = epi == EPI_ROPE ? g.D / 32 : 1;
   if (epi == EPI_ROPE) {
@@ -1013,7 +1070,7 @@ const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
 // Returns the candidates, cheapest first.
 std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
   const double FEED = 90e9, TENSOR = 1636e12 / 148.0, HBM = 6.5e12;
-  const int nk = (g.K + BK - 1) / BK;
+  const int nk = (g.K + (g.q8 ? 2 * BK : BK) - 1) / (g.q8 ? 2 * BK : BK);
   const int epi = epi_of(kind);
   const int out_bytes = epi == EPI_RESID ? 8 : (epi == EPI_F32 ? 4 : 2);
   const int nbf = epi == EPI_GATE_UP ? 2 : 1;
@@ -1048,7 +1105,7 @@ std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
   // takes in 128 rows of activations and half of each weight slice per K step. Clusters of
   // eight (a pair times four splits) measured 40-50 % slower than two splits at every decode
   // shape, so they are left to a forced plan.
-  if (g.M > BM && g.M <= 2 * BM && kind != K_MATMUL) {
+  if ((g.q8 || (g.M > BM && g.M <= 2 * BM)) && kind != K_MATMUL) {
     for (int bn : {256, 192, 128}) {
       for (int s = 1; s <= 2; s *= 2) {
         if (plan_error(kind, g, PAIR, bn, s)) continue;
@@ -1094,11 +1151,20 @@ int make_gemm(Ctx* c, Op& op) {
     if (s[0][1] <= 0 || s[0][1] % 8) return bad("K must be a positive multiple of 8 (use linear and rope_kv otherwise)");
     op.rope.H = (int)H, op.rope.G = (int)G, op.rope.D = (int)D, op.rope.NPOS = (int)s[4][0], op.rope.NS = (int)s[8][0];
   }
-  for (size_t i = 0; i < s.size() && op.kind != K_LINEAR_ROPE_KV; ++i)
+  const bool q8kind = op.kind == K_LINEAR_Q8 || op.kind == K_LINEAR_RESIDUAL_Q8 || op.kind == K_GATE_UP_Q8;
+  for (size_t i = 0; i < s.size() && op.kind != K_LINEAR_ROPE_KV && !q8kind; ++i)
     if (s[i].size() != 2 && !(op.kind == K_LINEAR_SCATTER && i == 2)) return bad("every array is two-dimensional");
+  if (q8kind && (s[0].size() != 2 || s[2].size() != 2)) return bad("Xq and Wq are two-dimensional");
   const GemmShape g = gemm_shape(op);
   if (op.kind == K_LINEAR_ROPE_KV) {
     // checked above
+  } else if (g.q8) {
+    const bool gu = op.kind == K_GATE_UP_Q8;
+    const size_t o = gu ? 6 : 4;
+    if (s[1].size() != 1 || s[1][0] != g.M || s[2].size() != 2 || s[2][1] != g.K || s[3].size() != 1 || s[3][0] != g.N ||
+        (gu && (s[4] != s[2] || s[5] != s[3])) || s[o].size() != 2 || s[o][0] != g.M || s[o][1] != g.N)
+      return bad("shapes are Xq[M,K], sx[M], Wq[N,K], sw[N], (Wuq[N,K], su[N],) Y[M,N]");
+    if (g.K <= 0 || g.K % 16 || g.N % 8) return bad("K must be a positive multiple of 16 and N a multiple of 8");
   } else if (op.kind == K_LINEAR_SCATTER) {
     if (s[1][1] != g.K || s[2].size() != 1 || (size_t)s[2][0] < sizeof(TpTable))
       return bad("shapes are X[M,K], W[N,K], table[bytes of tb200_tp_sizes]");
@@ -1145,6 +1211,13 @@ int launch_plan(Ctx* c, Op& op, const uint64_t* a, int mt, int bn, int splits) {
   if (op.kind == K_LINEAR_SCATTER) {
     op.aux = (int)(uint32_t)a[3];
     if (op.aux < 0 || op.aux > 1) return fail(c, op.name + ": which is 0 or 1");
+  }
+  if (g.q8) {
+    // Xq, sx, Wq, sw, (Wuq, su,) out
+    const bool gu = op.kind == K_GATE_UP_Q8;
+    op.q8[0] = (const float*)a[1], op.q8[1] = (const float*)a[3], op.q8[2] = gu ? (const float*)a[5] : nullptr;
+    return dispatch(c, op, op.kind, mt, bn, g, splits, (const void*)a[0], (const void*)a[2],
+                    gu ? (const void*)a[4] : nullptr, (void*)a[gu ? 6 : 4], false);
   }
   if (op.kind == K_LINEAR_ROPE_KV) {
     // X, W, pos, slot, C, S, QKV, Q, Kc, Vc, K, V

@@ -9,6 +9,7 @@
 // is rounded on its own (no fused multiply-add), so that the KV pages written
 // here are bit-identical to the reference's CPU path for identical inputs.
 #include <climits>
+#include <cuda_fp8.h>
 
 #include "common.cuh"
 
@@ -124,6 +125,112 @@ __global__ void rmsnorm_generic_kernel(const float* __restrict__ X, const int* _
   for (int c = threadIdx.x; c < Dm; c += blockDim.x) {
     const float v = in ? x[c] : 0.0f;
     Y[(size_t)b * Dm + c] = __float2half_rn(__fmul_rn(__fmul_rn(v, rs), __half2float(W[c])));
+  }
+}
+
+// ---- FP8 mode (no counterpart in the reference: a separate, non-parity mode) -------------------
+// A row of activations as E4M3 bytes and one f32 scale: scale = max|row| / 448 (1 for a zero
+// row), byte = e4m3(x / scale) rounded to nearest even and saturated, the same arithmetic as the
+// host's quantiser of the weights (tessel_b200/fp8.py), so both sides of a product are
+// quantised by one rule.
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < nw) ? red[l] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ unsigned char to_e4m3(float x) {
+  return (unsigned char)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
+}
+
+// quant_rows: X f16 [M, K] -> Q u8 [M, K], S f32 [M]. One block per row; K % 8 == 0.
+__global__ void quant_rows_kernel(const __half* __restrict__ X, unsigned char* __restrict__ Q, float* __restrict__ S,
+                                  int K) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float red[32];
+  const __half* x = X + (size_t)blockIdx.x * K;
+  float mx = 0.f;
+  for (int c = threadIdx.x * 8; c < K; c += blockDim.x * 8) {
+    H8 v;
+    v.u = *reinterpret_cast<const uint4*>(x + c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(__half2float(v.h[j])));
+  }
+  mx = block_max(mx, red);
+  const float scale = mx > 0.f ? __fdiv_rn(mx, 448.0f) : 1.0f;
+  if (threadIdx.x == 0) S[blockIdx.x] = scale;
+  unsigned char* q = Q + (size_t)blockIdx.x * K;
+  for (int c = threadIdx.x * 8; c < K; c += blockDim.x * 8) {
+    H8 v;
+    v.u = *reinterpret_cast<const uint4*>(x + c);
+    unsigned char b[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) b[j] = to_e4m3(__fdiv_rn(__half2float(v.h[j]), scale));
+    *reinterpret_cast<uint2*>(q + c) = *reinterpret_cast<const uint2*>(b);
+  }
+}
+
+// rmsnorm_q8: the RMSNorm of kernels/llm.tl:19-25 (y rounded to f16, as the reference's h is)
+// followed by quant_rows of y, in one pass: X f32 [T, Dm], W f16 [Dm] -> Q u8 [T, Dm], S f32 [T].
+template <int PER>  // float4 chunks per thread
+__global__ void rmsnorm_q8_kernel(const float* __restrict__ X, const __half* __restrict__ W,
+                                  unsigned char* __restrict__ Q, float* __restrict__ S, float eps, int Dm) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  const float* x = X + (size_t)b * Dm;
+  float4 v[PER];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = (threadIdx.x + i * blockDim.x) * 4;
+    v[i] = c < Dm ? *reinterpret_cast<const float4*>(x + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss += __fmul_rn(v[i].x, v[i].x);
+    ss += __fmul_rn(v[i].y, v[i].y);
+    ss += __fmul_rn(v[i].z, v[i].z);
+    ss += __fmul_rn(v[i].w, v[i].w);
+  }
+  const float sum = block_sum(ss, red);
+  const float ms = __fdiv_rn(sum, (float)Dm);
+  const float rs = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(ms, eps)));
+  float mx = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = (threadIdx.x + i * blockDim.x) * 4;
+    if (c < Dm) {
+      const __half2 w01 = *reinterpret_cast<const __half2*>(W + c);
+      const __half2 w23 = *reinterpret_cast<const __half2*>(W + c + 2);
+      // y as the f16 the unquantised path would have stored
+      v[i].x = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i].x, rs), __low2float(w01))));
+      v[i].y = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i].y, rs), __high2float(w01))));
+      v[i].z = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i].z, rs), __low2float(w23))));
+      v[i].w = __half2float(__float2half_rn(__fmul_rn(__fmul_rn(v[i].w, rs), __high2float(w23))));
+      mx = fmaxf(fmaxf(mx, fmaxf(fabsf(v[i].x), fabsf(v[i].y))), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+    }
+  }
+  mx = block_max(mx, red);
+  const float scale = mx > 0.f ? __fdiv_rn(mx, 448.0f) : 1.0f;
+  if (threadIdx.x == 0) S[b] = scale;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int c = (threadIdx.x + i * blockDim.x) * 4;
+    if (c < Dm) {
+      uchar4 o;
+      o.x = to_e4m3(__fdiv_rn(v[i].x, scale));
+      o.y = to_e4m3(__fdiv_rn(v[i].y, scale));
+      o.z = to_e4m3(__fdiv_rn(v[i].z, scale));
+      o.w = to_e4m3(__fdiv_rn(v[i].w, scale));
+      *reinterpret_cast<uchar4*>(Q + (size_t)b * Dm + c) = o;
+    }
   }
 }
 
@@ -515,6 +622,15 @@ int make_glue(Ctx* c, Op& op) {
       if (s[0].size() != 3 || s[0][2] != 2 || s[1].size() != 1 || s[1][0] != s[0][1] || s[0][0] < 1)
         return bad("shapes are pairs[R,M,2], out[M]");
       break;
+    case K_QUANT_ROWS:
+      if (s[0].size() != 2 || s[1] != s[0] || s[2].size() != 1 || s[2][0] != s[0][0] || s[0][1] % 8)
+        return bad("shapes are X[M,K], Q[M,K], S[M] with K a multiple of 8");
+      break;
+    case K_RMSNORM_Q8:
+      if (s[0].size() != 2 || s[1].size() != 1 || s[1][0] != s[0][1] || s[2] != s[0] || s[3].size() != 1 ||
+          s[3][0] != s[0][0] || s[0][1] % 4 || s[0][1] > 8192)
+        return bad("shapes are X[T,Dm], W[Dm], Q[T,Dm], S[T] with Dm a multiple of 4, at most 8192");
+      break;
     case K_DECODE_ADVANCE:
       if (s[5].size() != 2 || s[5][0] != s[0][0] || s[6].size() != 2 || s[6][1] != s[0][0])
         return bad("shapes are picked[T], tok[T], pos[T], slot[T], lens[T], table[T,MP], hist[S,T]");
@@ -527,7 +643,6 @@ int make_glue(Ctx* c, Op& op) {
 
 int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
   const auto& s = op.shapes;
-  cudaStream_t st = c->stream;
   switch (op.kind) {
     case K_EMBED: {
       const int T = (int)s[0][0], V = (int)s[1][0], Dm = (int)s[1][1];
@@ -615,6 +730,32 @@ int launch_glue(Ctx* c, Op& op, const uint64_t* a) {
       const int R = (int)s[0][0], M = (int)s[0][1];
       if (M == 0) return 0;
       TB_CUDA(c, launch_k(c, argmax_merge_kernel, dim3((M + 127) / 128), dim3(128), 0, 1, (const float*)a[0], (int*)a[1], M, R));
+      break;
+    }
+    case K_QUANT_ROWS: {
+      const int M = (int)s[0][0], K = (int)s[0][1];
+      if (M == 0 || K == 0) return 0;
+      TB_CUDA(c, launch_k(c, quant_rows_kernel, dim3(M), dim3(256), 0, 1, (const __half*)a[0], (unsigned char*)a[1],
+                          (float*)a[2], K));
+      break;
+    }
+    case K_RMSNORM_Q8: {
+      const int T = (int)s[0][0], Dm = (int)s[0][1];
+      if (T == 0) return 0;
+      const float* X = (const float*)a[0];
+      const __half* W = (const __half*)a[1];
+      unsigned char* Q = (unsigned char*)a[2];
+      float* S = (float*)a[3];
+      const float eps = bits_f32(a[4]);
+      const int chunks = Dm / 4;
+      if (chunks <= 256)
+        TB_CUDA(c, launch_k(c, rmsnorm_q8_kernel<1>, dim3(T), dim3(256), 0, 1, X, W, Q, S, eps, Dm));
+      else if (chunks <= 512)
+        TB_CUDA(c, launch_k(c, rmsnorm_q8_kernel<2>, dim3(T), dim3(256), 0, 1, X, W, Q, S, eps, Dm));
+      else if (chunks <= 1024)
+        TB_CUDA(c, launch_k(c, rmsnorm_q8_kernel<4>, dim3(T), dim3(256), 0, 1, X, W, Q, S, eps, Dm));
+      else
+        TB_CUDA(c, launch_k(c, rmsnorm_q8_kernel<8>, dim3(T), dim3(256), 0, 1, X, W, Q, S, eps, Dm));
       break;
     }
     case K_DECODE_ADVANCE: {

@@ -132,14 +132,22 @@ class Engine:
     """``w`` holds the full model; with ``nranks > 1`` this engine keeps rank ``rank``'s shard of it."""
 
     def __init__(self, gpu: Gpu, w: Weights, lim: Limits, rank: int = 0, nranks: int = 1, sharded: bool = False,
-                 exchange=None):
+                 exchange=None, fp8: bool = False):
         """``sharded``: ``w`` already is this rank's shard (its ``cfg`` the local shape).
         ``exchange``: with ``nranks > 1``, a function that takes this rank's list of byte strings and
         returns every rank's list (an all-gather on the host). When given, the ranks map each
         other's buffers and the cross-rank sum after o_proj and down_proj runs fused with the
         residual add and the next RMSNorm in one kernel over NVLink (``tp_reduce_norm``) instead
-        of linear_f32 -> NCCL allreduce -> residual_add -> rmsnorm."""
+        of linear_f32 -> NCCL allreduce -> residual_add -> rmsnorm.
+        ``fp8``: a separate, NON-PARITY mode (single rank): the five projection matrices of every
+        layer are quantised to E4M3 with one f32 scale per output row when they are uploaded,
+        activations are quantised per row on the device in front of each projection, and the
+        projections run on the tensor cores' 8-bit path. Attention, RoPE, the cache, the norms'
+        arithmetic and the LM head stay as they are."""
         full = w.cfg
+        if fp8 and nranks != 1:
+            raise ValueError("the FP8 mode runs on a single rank")
+        self.fp8 = fp8
         if full.heads % full.kv_heads or full.head_dim % 2:
             raise ValueError("heads must be a multiple of kv_heads, head_dim even")
         if not sharded:
@@ -172,7 +180,20 @@ class Engine:
         slots = lim.pages * lim.page
         kv_bytes = slots * cfg.kv_heads * cfg.head_dim * 2
         self.layers: List[_DevLayer] = []
+        self.q8: List[Dict[str, Buf]] = []
         for l in w.layers:
+            if fp8:
+                # E4M3 bytes and row scales instead of the f16 matrices (which are not uploaded).
+                from . import fp8 as f8
+                q = {}
+                for name in ("wqkv", "wo", "wg", "wu", "wd"):
+                    bytes_, scale = f8.quantize_rows(np.asarray(getattr(l, name), np.float32))
+                    q[name], q[name + "_s"] = up(bytes_), up(scale)
+                self.q8.append(q)
+                none = Buf(0, 0)
+                self.layers.append(_DevLayer(up(l.attn_norm), none, none, up(l.mlp_norm), none, none, none,
+                                             gpu.alloc(kv_bytes), gpu.alloc(kv_bytes)))
+                continue
             self.layers.append(_DevLayer(up(l.attn_norm), up(l.wqkv), up(l.wo), up(l.mlp_norm), up(l.wg), up(l.wu),
                                          up(l.wd), gpu.alloc(kv_bytes), gpu.alloc(kv_bytes)))
         c, s = rope_tables(cfg)
@@ -201,6 +222,11 @@ class Engine:
         # Page-locked staging for a step's inputs and results.
         mp = lim.max_seq_pages
         self._stage = gpu.host_array((6 * t + t * mp,), np.int32)
+        if fp8:
+            # Quantised activations in front of the projections: bytes and one scale per row.
+            self.hq, self.hs = a(t * cfg.dim), a(t * 4)
+            self.oq, self.os = a(t * hd), a(t * 4)
+            self.mq, self.ms = a(t * cfg.ffn), a(t * 4)
         self.meta = a(t * 4 * 4)  # chunk descriptors of a mixed step: (row0, nrows, pos0, -)
         self._meta_stage = gpu.host_array((t, 4), np.int32)
         self._chunks = 0
@@ -447,6 +473,20 @@ class Engine:
         k = g.kernel
         embed = k("embed", [[t], [v, dm], [t, dm]])
         norm = k("rmsnorm", [[t, dm], [dm], [t, dm]])
+        if prefill:
+            att = k("prefill_attention", [[t, nh, hd], [t, ng, hd], [t, ng, hd], [t], [t, nh, hd]])
+        else:
+            att = k("decode_attention", [[t, nh, hd], [lim.pages, lim.page, ng, hd], [lim.pages, lim.page, ng, hd],
+                                         [t, mp], [t], [t, nh, hd]])
+        chunk_att = None
+        if not prefill and self._chunks:
+            cache = [lim.pages, lim.page, ng, hd]
+            chunk_att = k("chunk_attention", [[t, nh, hd], cache, cache, [t, mp], [self._chunks, 4], [t, nh, hd]])
+        if self.fp8:
+            g.launch(embed, [self.tok, self.embed, self.x])
+            self._launch_layers_q8(t, prefill, att, chunk_att, eps, scale)
+            self._launch_head(t, bw, greedy, eps)
+            return
         l0 = self.layers[0]
         rope_shapes = [[t], [t], [npos, hd // 2], [npos, hd // 2]]
         kv_shapes = [[t, nh, hd], [ns, ng, hd], [ns, ng, hd], [t, ng, hd], [t, ng, hd]]
@@ -462,15 +502,6 @@ class Engine:
             qkv = self._mm("linear", [[t, dm], [w, dm], [t, w]], [self.h, l0.wqkv, self.qkv], t)
             # rope_q and kv_write of the reference (src/llm/engine.rs:391-418) run as one launch.
             ropekv = k("rope_kv", [[t, w]] + rope_shapes + kv_shapes)
-        if prefill:
-            att = k("prefill_attention", [[t, nh, hd], [t, ng, hd], [t, ng, hd], [t], [t, nh, hd]])
-        else:
-            att = k("decode_attention", [[t, nh, hd], [lim.pages, lim.page, ng, hd], [lim.pages, lim.page, ng, hd],
-                                         [t, mp], [t], [t, nh, hd]])
-        chunk_att = None
-        if not prefill and self._chunks:
-            cache = [lim.pages, lim.page, ng, hd]
-            chunk_att = k("chunk_attention", [[t, nh, hd], cache, cache, [t, mp], [self._chunks, 4], [t, nh, hd]])
         gu = self._mm("gate_up", [[t, dm], [f, dm], [f, dm], [t, f]], [self.h, l0.wg, l0.wu, self.mlp], t)
         if self.tp_table is not None and self.fused:
             # Each row of a partial product goes straight into its owner rank's inbox.
@@ -523,6 +554,39 @@ class Engine:
             return
         g.launch(qkv, [self.h, l.wqkv, self.qkv])
         g.launch(ropekv, [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l.kc, l.vc, self.k, self.v])
+
+    def _launch_layers_q8(self, t, prefill, att, chunk_att, eps, scale) -> None:
+        """The decoder layers in the FP8 mode: rmsnorm_q8 / quant_rows hand E4M3 rows and their
+        scales to linear_q8, gate_up_q8 and linear_residual_q8; the rest of a layer is unchanged."""
+        cfg, lim, g, k = self.cfg, self.lim, self.gpu, self.gpu.kernel
+        dm, nh, ng, hd = cfg.dim, cfg.heads, cfg.kv_heads, cfg.head_dim
+        w, f = cfg.qkv(), cfg.ffn
+        ns, npos = lim.pages * lim.page, cfg.max_pos
+        normq = k("rmsnorm_q8", [[t, dm], [dm], [t, dm], [t]])
+        qkv = k("linear_q8", [[t, dm], [t], [w, dm], [w], [t, w]])
+        ropekv = k("rope_kv", [[t, w], [t], [t], [npos, hd // 2], [npos, hd // 2], [t, nh, hd], [ns, ng, hd],
+                               [ns, ng, hd], [t, ng, hd], [t, ng, hd]])
+        quant_o = k("quant_rows", [[t, nh * hd], [t, nh * hd], [t]])
+        oproj = k("linear_residual_q8", [[t, nh * hd], [t], [dm, nh * hd], [dm], [t, dm]])
+        gu = k("gate_up_q8", [[t, dm], [t], [f, dm], [f], [f, dm], [f], [t, f]])
+        quant_m = k("quant_rows", [[t, f], [t, f], [t]])
+        down = k("linear_residual_q8", [[t, f], [t], [dm, f], [dm], [t, dm]])
+        for l, q in zip(self.layers, self.q8):
+            g.launch(normq, [self.x, l.n1, self.hq, self.hs, eps])
+            g.launch(qkv, [self.hq, self.hs, q["wqkv"], q["wqkv_s"], self.qkv])
+            g.launch(ropekv, [self.qkv, self.pos, self.slot, self.cos, self.sin, self.q, l.kc, l.vc, self.k, self.v])
+            if prefill:
+                g.launch(att, [self.q, self.k, self.v, self.starts, self.o, scale])
+            else:
+                g.launch(att, [self.q, l.kc, l.vc, self.table, self.lens, self.o, scale])
+                if chunk_att is not None:
+                    g.launch(chunk_att, [self.q, l.kc, l.vc, self.table, self.meta, self.o, scale])
+            g.launch(quant_o, [self.o, self.oq, self.os])
+            g.launch(oproj, [self.oq, self.os, q["wo"], q["wo_s"], self.x])
+            g.launch(normq, [self.x, l.n2, self.hq, self.hs, eps])
+            g.launch(gu, [self.hq, self.hs, q["wg"], q["wg_s"], q["wu"], q["wu_s"], self.mlp])
+            g.launch(quant_m, [self.mlp, self.mq, self.ms])
+            g.launch(down, [self.mq, self.ms, q["wd"], q["wd_s"], self.x])
 
     def _launch_layers_fused(self, t, prefill, norm, qkv, ropekv, att, oproj, gu, down, eps, scale, chunk_att=None) -> None:
         """The decoder layers under tensor parallelism with the fused cross-rank reduction: o_proj

@@ -137,6 +137,8 @@ class EmuGpu:
             kc, vc, kd, vd = oracle.kv_write(qkv, A(2, i), A(3, i), A(4, f), A(5, f), A(8, h), A(9, h), sh[8][1],
                                              sh[8][2])
             A(8, h)[:], A(9, h)[:], A(10, h)[:], A(11, h)[:] = kc, vc, kd, vd
+        elif name in ("quant_rows", "rmsnorm_q8", "linear_q8", "linear_residual_q8", "gate_up_q8"):
+            self._q8(name, A, sc)
         elif name == "prefill_attention":
             A(4, h)[:] = oracle.prefill_attention(A(0, h), A(1, h), A(2, h), A(3, i), sc(5))
         elif name == "flash_attention":
@@ -183,6 +185,30 @@ class EmuGpu:
                 out[m] = 0 if best[1] < 0 else int(best[1])
         else:
             raise GpuError(f"no kernel {name}")
+
+    @staticmethod
+    def _q8(name, A, sc) -> None:
+        """The FP8 mode's kernels in numpy: the device's quantiser rule (tessel_b200/fp8.py), exact
+        products of the decoded bytes summed in f64, scaled back in f32 as the epilogue does."""
+        from tessel_b200 import fp8
+        h, f, u8 = np.float16, np.float32, np.uint8
+
+        def product(xq, sx, wq, sw):
+            acc = (fp8.decode(xq).astype(np.float64) @ fp8.decode(wq).astype(np.float64).T).astype(f)
+            return acc * (sx[:, None] * sw[None, :])
+
+        if name == "quant_rows":
+            A(1, u8)[:], A(2, f)[:] = fp8.quantize_rows(A(0, h).astype(f))
+        elif name == "rmsnorm_q8":
+            A(2, u8)[:], A(3, f)[:] = fp8.quantize_rows(oracle.rmsnorm(A(0, f), A(1, h), sc(4)).astype(f))
+        elif name == "linear_q8":
+            A(4, h)[:] = product(A(0, u8), A(1, f), A(2, u8), A(3, f)).astype(h)
+        elif name == "linear_residual_q8":
+            A(4, f)[:] = A(4, f) + product(A(0, u8), A(1, f), A(2, u8), A(3, f))
+        else:
+            g = product(A(0, u8), A(1, f), A(2, u8), A(3, f))
+            u = product(A(0, u8), A(1, f), A(4, u8), A(5, f))
+            A(6, h)[:] = ((g / (f(1) + np.exp(-g))) * u).astype(h)
 
     def allreduce(self, b: Buf, count: int, dtype: int = 0) -> None:
         if self._capturing:

@@ -71,6 +71,29 @@ def test_bf16_and_f32_are_rounded_to_nearest_even(tmp_path):
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
 
 
+def test_fp8_checkpoint_is_dequantised_with_its_row_scales(tmp_path):
+    """Beyond the reference: projection matrices stored as F8_E4M3 with a "<name>_scale" tensor
+    (one f32 per output row) load as f16(decode(bytes) * scale); a rank's shard takes its rows'
+    scales; everything that is not a projection is stored and read as F16."""
+    from tessel_b200 import fp8
+    cfg = Config(dim=64, layers=2, heads=8, kv_heads=4, head_dim=16, ffn=128, vocab=256, max_pos=256)
+    w = Weights.random(cfg, 6)
+    checkpoint.save(w, str(tmp_path), "F8_E4M3")
+    got = checkpoint.load(str(tmp_path))
+    assert np.array_equal(got.embed, w.embed) and np.array_equal(got.norm, w.norm)
+    for a, b in zip(got.layers, w.layers):
+        assert np.array_equal(a.attn_norm, b.attn_norm)
+        for name in ("wqkv", "wo", "wg", "wu", "wd"):
+            x, y = getattr(a, name).astype(np.float32), getattr(b, name).astype(np.float32)
+            assert np.abs(x - y).max() <= np.abs(y).max() / 14.0, name       # three mantissa bits
+            assert np.abs(x - y).max() > 0, name
+    # wo is stored whole and quantised by its own rows: the reader must reproduce exactly that.
+    q, sc = fp8.quantize_rows(w.layers[0].wo.astype(np.float32))
+    assert np.array_equal(got.layers[0].wo, (fp8.decode(q) * sc[:, None]).astype(np.float16))
+    shard = checkpoint.load(str(tmp_path), 1, 2)
+    assert np.array_equal(shard.layers[1].wg, got.layers[1].wg[cfg.ffn // 2:])
+
+
 def test_sharded_files_and_config_defaults(tmp_path):
     """Tensors spread over the files of a model.safetensors.index.json; config.json with the
     optional keys absent and a list of end tokens."""
