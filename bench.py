@@ -68,6 +68,9 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-micro", action="store_true", help="skip the single-kernel numbers (N = 1)")
     ap.add_argument("--profile-steps", type=int, default=2)
+    ap.add_argument("--fp8", action="store_true",
+                    help="N = 1: the NON-PARITY FP8 mode (E4M3 projections); the line says so in `dtype` "
+                         "and is not the headline number")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the device-resident timed region with cudaProfilerStart/Stop "
                          "(for `ncu --profile-from-start off`)")
@@ -221,7 +224,8 @@ def config_of(args, wl, world, seqs, plens):
     Hl, Gl, Fl, D = cfg.heads // world, cfg.kv_heads // world, cfg.ffn // world, cfg.head_dim
     vocab_parallel = world > 1 and cfg.vocab % world == 0 and cfg.vocab <= 1 << 24
     head_rows = cfg.vocab // world if vocab_parallel else cfg.vocab
-    wbytes = 2.0 * (cfg.layers * ((Hl + 2 * Gl) * D * cfg.dim + cfg.dim * Hl * D + 3 * Fl * cfg.dim) + head_rows * cfg.dim)
+    layer_w = cfg.layers * ((Hl + 2 * Gl) * D * cfg.dim + cfg.dim * Hl * D + 3 * Fl * cfg.dim)
+    wbytes = (1.0 if getattr(args, "fp8", False) else 2.0) * layer_w + 2.0 * head_rows * cfg.dim
     kvbytes = 4.0 * Gl * D * cfg.layers * ctx_mid * seqs
     par = f"tp{world}" + (f" ({args.tp_exchange} exchange)" if world > 1 else "")
     return ({"workload": wl["label"], "sequences": int(seqs), "parallelism": par,
@@ -376,8 +380,10 @@ def run_ours(args, wl):
             everyone = [None] * world
             dist.all_gather_object(everyone, mine)
             return everyone
+    if args.fp8 and world > 1:
+        raise SystemExit("--fp8 runs on one GPU")
     e = Engine(gpu, w, Limits(page=P, pages=pages, max_tokens=max_prompt, max_seq_pages=msp), rank=rank,
-               nranks=world, sharded=True, exchange=exchange)
+               nranks=world, sharded=True, exchange=exchange, fp8=args.fp8)
     e.fused = world > 1 and args.tp_exchange == "fused"
     s = Scheduler(e, reqs, seqs, packed=True, device_argmax=True)
 
@@ -496,7 +502,8 @@ def run_ours(args, wl):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(Wm, 3),
         "ms_per_step": dev_step_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "f16", "data": "synthetic", "config": config,
+        "dtype": "f8e4m3 projections, f16 elsewhere (non-parity mode)" if args.fp8 else "f16", "data": "synthetic",
+        "config": config,
         "e2e": {"value": n * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * n,
                 "ms_per_step": e2e_ms / K, "ms_per_step_min": min(e2e_all) / K, "ms_per_step_max": max(e2e_all) / K,
                 "repeats": E2E_REPEATS, "value_is": "median of the repeats"},

@@ -187,8 +187,16 @@ class Engine:
                 from . import fp8 as f8
                 q = {}
                 for name in ("wqkv", "wo", "wg", "wu", "wd"):
-                    bytes_, scale = f8.quantize_rows(np.asarray(getattr(l, name), np.float32))
-                    q[name], q[name + "_s"] = up(bytes_), up(scale)
+                    m = getattr(l, name)
+                    if isinstance(m, np.ndarray):
+                        bytes_, scale = f8.quantize_rows(m.astype(np.float32))
+                        q[name], q[name + "_s"] = up(bytes_), up(scale)
+                    else:
+                        # Already on the device: the same rule, by the kernel that quantises activations.
+                        rows, cols = m.shape
+                        q[name], q[name + "_s"] = gpu.alloc(rows * cols), gpu.alloc(rows * 4)
+                        gpu.launch(gpu.kernel("quant_rows", [[rows, cols], [rows, cols], [rows]]),
+                                   [up(m), q[name], q[name + "_s"]])
                 self.q8.append(q)
                 none = Buf(0, 0)
                 self.layers.append(_DevLayer(up(l.attn_norm), none, none, up(l.mlp_norm), none, none, none,
