@@ -451,6 +451,9 @@ class Engine:
         if self.tune and t <= self.tune_rows and getattr(g, "tuned", None) is not None:
             l0 = self.layers[0]
             kf, kp = g.kernel("linear_rope_kv", fused_shapes), g.kernel("linear", [[t, dm], [w, dm], [t, w]])
+            if kf.id in g.fusion:   # decided by an earlier engine on this context: same kernels, same plans
+                self._fuse_by_rows[t] = g.fusion[kf.id]
+                return g.fusion[kf.id]
             g.tuned[kf.id] = g.tune(kf, fused_args)
             g.tuned[kp.id] = g.tune(kp, [self.h, l0.wqkv, self.qkv])
             fused_us, plain_us = g.tuned[kf.id][1], g.tuned[kp.id][1]
@@ -465,6 +468,7 @@ class Engine:
             rope_us = g.time_end() * 1000.0 / 8
             if fused_us > 0 and plain_us > 0:
                 choice = fused_us < plain_us + rope_us
+            g.fusion[kf.id] = choice
         self._fuse_by_rows[t] = choice
         return choice
 

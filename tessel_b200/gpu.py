@@ -75,6 +75,7 @@ class Gpu:
         self._phase = ""
         # Kernels whose tiles were chosen by timing (``tune``): id -> ((MT, BN, splits), microseconds).
         self.tuned: Dict[int, tuple] = {}
+        self.fusion: Dict[int, bool] = {}   # fused-kernel id -> whether the engine's timing preferred it
 
     # -- plumbing --------------------------------------------------------------
     def _check(self, rc: int) -> None:
