@@ -93,9 +93,23 @@ int tb200_host_free(tb200_ctx* ctx, void* ptr);
  * positions meta[c][2], meta[c][2] + 1, ... of their sequence, whose block
  * table is row meta[c][0] of `table`; row r attends to cache positions 0 to
  * its own, this step's keys included (kv_write runs first). Rows outside every
- * chunk are not written. The
- * reference's `meta` and `warps` arguments have no equivalent: tile shapes are
- * chosen inside. */
+ * chunk are not written.
+ *
+ * FP8 mode (no counterpart in the reference, which computes in f16; results
+ * differ from the f16 kernels by the quantisation): E4M3 bytes with one f32
+ * scale per row, value = decode(byte) * scale, scale = max|row| / 448 (1 for a
+ * row of zeros), rounding to nearest even, saturating. quant_rows (X f16[M,K],
+ * Q u8[M,K], S f32[M]; K a multiple of 8) quantises rows; rmsnorm_q8 (X
+ * f32[T,Dm], W f16[Dm], Q u8[T,Dm], S f32[T], then the f32 eps) is rmsnorm
+ * followed by quant_rows of its f16 result, in one launch. linear_q8 and
+ * linear_residual_q8 (Xq u8[M,K], sx f32[M], Wq u8[N,K], sw f32[N], Y[M,N] f16
+ * / f32 accumulated into) and gate_up_q8 (Xq, sx, Wgq, sg, Wuq, su, Y
+ * f16[M,F]) are linear, linear_residual and gate_up on the 8-bit tensor-core
+ * path with f32 accumulation, the product scaled by sx[row] * sw[column] before
+ * the epilogue's own arithmetic; K a multiple of 16, N a multiple of 8.
+ *
+ * The reference's `meta` and `warps` arguments have no equivalent: tile shapes
+ * are chosen inside. */
 int tb200_kernel(tb200_ctx* ctx, const char* name, const int64_t* shapes, const int32_t* ranks, int n_arrays,
                  tb200_op* out);
 
