@@ -4,8 +4,8 @@ the single-rank run of the SAME model.
 One rank of an ``nranks``-way run calls :func:`run`; every rank shards the same full weights
 (``Weights.random`` with a fixed seed), so the logits, the greedy tokens and the KV pages of a
 run over N ranks can be held against those of one rank: logits within 2e-3 of the largest,
-32 greedy decode steps with the same tokens, pages equal to the single-rank pages sliced
-along the KV-head axis, and the normalised activations h (and the final residual stream x)
+32 greedy decode steps with the same tokens (also with a prompt fed in chunks beside the decodes), pages equal to the
+single-rank pages sliced along the KV-head axis, and the normalised activations h (and the final residual stream x)
 the same bits on every rank. The tests drive it on the CPU stand-in and on GPUs; the benchmark
 prints its summary beside a multi-GPU number (:func:`summary`).
 
@@ -37,11 +37,21 @@ def requests(cfg: Config) -> List[Request]:
     return [Request(g.integers(0, cfg.vocab, n).tolist(), DECODE_STEPS + 1) for n in (40, 7, 33)]
 
 
+CHUNK, CHUNK_NEW = 32, 8
+
+
+def chunk_requests(cfg: Config) -> List[Request]:
+    """A short prompt and one of 100 tokens, which is fed 32 tokens at a time beside the decodes."""
+    g = np.random.default_rng(3)
+    return [Request(g.integers(0, cfg.vocab, n).tolist(), CHUNK_NEW) for n in (9, 100)]
+
+
 def run(gpu, rank: int, nranks: int, exchange: Optional[Callable] = None) -> Dict[str, np.ndarray]:
-    """Two packed prompts, one decode step, and a 3-request greedy generation of 1 + 32 tokens on
-    rank ``rank`` of ``nranks``. Returns the prefill logits ``pre`` [2, vocab], the decode step's
-    logits ``dec`` [2, vocab], layer 1's cache shard ``kc``/``vc``, the real rows of x and h after
-    the decode step, and ``tokens`` [3, 33]."""
+    """Two packed prompts, one decode step, a 3-request greedy generation of 1 + 32 tokens, and a
+    2-request generation with one prompt fed in chunks, on rank ``rank`` of ``nranks``. Returns
+    the prefill logits ``pre`` [2, vocab], the decode step's logits ``dec`` [2, vocab], layer 1's
+    cache shard ``kc``/``vc``, the real rows of x and h after the decode step, ``tokens`` [3, 33]
+    and ``chunk_tokens`` [2, 8]."""
     cfg, w = model()
     lim = Limits(page=16, pages=40, max_tokens=128, max_seq_pages=8)
     e = Engine(gpu, w, lim, rank=rank, nranks=nranks, exchange=exchange)
@@ -58,7 +68,11 @@ def run(gpu, rank: int, nranks: int, exchange: Optional[Callable] = None) -> Dic
     e2 = Engine(gpu, w, Limits(page=16, pages=64, max_tokens=128, max_seq_pages=8), rank=rank, nranks=nranks,
                 exchange=exchange)
     outs, _ = generate_with(e2, requests(cfg), 3, True, device_argmax=True)
-    return dict(pre=pre, dec=dec, kc=kc, vc=vc, x=x, h=h, tokens=np.asarray([o.tokens for o in outs]))
+    e3 = Engine(gpu, w, Limits(page=16, pages=64, max_tokens=64, max_seq_pages=8), rank=rank, nranks=nranks,
+                exchange=exchange)
+    couts, _ = generate_with(e3, chunk_requests(cfg), 2, True, device_argmax=True, chunk=CHUNK)
+    return dict(pre=pre, dec=dec, kc=kc, vc=vc, x=x, h=h, tokens=np.asarray([o.tokens for o in outs]),
+                chunk_tokens=np.asarray([o.tokens for o in couts]))
 
 
 def rel_err(got: np.ndarray, want: np.ndarray) -> float:
@@ -97,6 +111,7 @@ def summary(one: Dict[str, np.ndarray], shards: List[Dict[str, np.ndarray]], dig
         "tokens_equal": int(min(steps, max(0, first_bad - 1))) if first_bad < same.shape[1] else int(steps),
         "decode_steps": int(steps),
         "h_bit_identical": len(set(digests)) == 1,
+        "chunked_prompt_tokens_equal": bool(np.array_equal(np.asarray(one["chunk_tokens"]), np.asarray(mine["chunk_tokens"]))),
     }
     worst, same_pages = 0.0, True
     for name in ("kc", "vc"):

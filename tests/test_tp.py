@@ -38,14 +38,14 @@ def launch(mode, world, tmp):
     return [dict(np.load(o)) for o in outs]
 
 
-def same_tokens_up_to_near_ties(ta, tb):
+def same_tokens_up_to_near_ties(ta, tb, requests, count):
     """Greedy tokens agree; where two runs part ways, the two choices' logits are a near-tie
     (a different summation order may flip it, as tests/llm.rs:57-78 allows), judged on the f32
     one-sequence model, and the comparison of that sequence ends there."""
     import oracle
     cfg, w = tpcheck.model()
-    for r, x, y in zip(tpcheck.requests(cfg), ta, tb):
-        assert len(x) == len(y) == tpcheck.DECODE_STEPS + 1
+    for r, x, y in zip(requests, ta, tb):
+        assert len(x) == len(y) == count
         for i, (u, v) in enumerate(zip(x, y)):
             if u == v:
                 continue
@@ -58,7 +58,9 @@ def compare(one, many):
     a, b = one[0], many[0]
     assert tpcheck.rel_err(b["pre"], a["pre"]) <= TOL
     assert tpcheck.rel_err(b["dec"], a["dec"]) <= TOL
-    same_tokens_up_to_near_ties(a["tokens"], b["tokens"])
+    cfg, _ = tpcheck.model()
+    same_tokens_up_to_near_ties(a["tokens"], b["tokens"], tpcheck.requests(cfg), tpcheck.DECODE_STEPS + 1)
+    same_tokens_up_to_near_ties(a["chunk_tokens"], b["chunk_tokens"], tpcheck.chunk_requests(cfg), tpcheck.CHUNK_NEW)
     # Rank r holds KV heads [r G/n, (r+1) G/n): gathered along the KV-head axis they are the 1-rank cache.
     for name in ("kc", "vc"):
         full = a[name].astype(np.float32)
