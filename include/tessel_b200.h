@@ -200,35 +200,43 @@ int tb200_allreduce(tb200_ctx* ctx, uint64_t dptr, size_t count, int dtype);
  * and the next RMSNorm, over peer memory (NVLink stores; every wait polls local
  * memory) instead of an NCCL call. Row r of a step belongs to rank r % nranks.
  * Each rank allocates two inboxes f32[nranks][ceil(T/nranks)][dim] (allocate
- * (T + nranks) * dim * 4 bytes), its residual stream x f32[T,dim], h f16[T,dim],
- * a landing area of T*dim*8 bytes (where the other owners' finished rows arrive
- * as 8-byte units {payload, call counter}), a flag area and an epoch area
- * (tb200_tp_sizes; landing area, flags and epochs zero-filled, as tb200_alloc
- * leaves them), exports them with tb200_ipc_export (a 64-byte handle each), the
- * host hands every rank the others' handles, tb200_ipc_import maps them, and
- * tb200_tp_table writes the table (pointer arrays indexed by rank; a rank's own
- * entries are its local pointers; `part0`/`part1` are the inboxes, `stage` the
- * landing areas) that the host then uploads to device memory.
+ * (T + nranks) * dim * 4 bytes each) and a landing area of T*dim*4 bytes (where
+ * the other owners' finished rows arrive), FILLS ALL THREE WITH 0xff BYTES
+ * (tb200_memset) - the 32-bit pattern 0xffffffff marks a word that holds
+ * nothing; the kernels wait for a word to differ from it, and put it back into
+ * every word they have consumed, so the fill is needed once - and exports them
+ * with tb200_ipc_export (a 64-byte handle each); the host hands every rank the
+ * others' handles, tb200_ipc_import maps them, and tb200_tp_table writes the
+ * table (`inbox0`, `inbox1`, `landing`: arrays indexed by rank, a rank's own
+ * entry its local pointer; `x` f32[T,dim] and `h` f16[T,dim]: this rank's own
+ * residual stream and normalised activations; `trace`: 0, or for a trace build
+ * of the library a zero-filled buffer of tb200_tp_sizes' trace size) that the
+ * host then uploads to device memory.
  *
  * The kernel "linear_scatter" (arrays: X f16[M,K], W f16[N,K], table u8[bytes];
  * then which i32) is linear_f32 whose output row r is stored into inbox `which`
  * of rank r % nranks, at [this rank][r / nranks] - the reduce-scatter, done by
  * the projection itself. The kernel "tp_reduce_norm" (arrays: table u8[bytes],
  * W f16[dim], X f32[T,dim]; then eps f32, which i32 = the inbox to sum, do_norm
- * i32, nranks i32) runs behind it: it waits until every rank's projection is
- * complete, adds the nranks partials of the rows this rank owns, in rank order,
- * to x and, if do_norm, normalises them into h, sends the rows to every peer
+ * i32, nranks i32) runs behind it: for each row this rank owns it waits until
+ * the nranks partials have arrived in its inbox, adds them, in rank order, to x
+ * and, if do_norm, normalises the row into h; it sends the rows to every peer
  * and collects the peers', which leaves h identical on every rank (x is then
  * current only in the rows this rank owns); with do_norm = 0 it leaves x
  * identical on every rank instead. Every rank must launch both the same number
- * of times with the same shapes. */
+ * of times with the same shapes, and consecutive pairs must alternate `which`
+ * (a rank may write into an inbox again only after the call that read it and
+ * one more have passed: the alternation guarantees it). A wait that does not
+ * end within a second raises the status word (401: partials, 402: rows) and the
+ * kernel returns; the exchange buffers are then in an undefined state. */
 #define TB200_IPC_HANDLE_BYTES 64
 int tb200_ipc_export(tb200_ctx* ctx, uint64_t dptr, void* handle);
 int tb200_ipc_import(tb200_ctx* ctx, const void* handle, uint64_t* dptr);
-int tb200_tp_sizes(size_t* table_bytes, size_t* flag_bytes, size_t* epoch_bytes);
-int tb200_tp_table(tb200_ctx* ctx, void* host_out, size_t bytes, int rank, int nranks, const uint64_t* part0,
-                   const uint64_t* part1, const uint64_t* x, const uint64_t* h, const uint64_t* stage,
-                   const uint64_t* flags, uint64_t epoch);
+int tb200_tp_sizes(size_t* table_bytes, size_t* trace_bytes);
+int tb200_tp_table(tb200_ctx* ctx, void* host_out, size_t bytes, int rank, int nranks, const uint64_t* inbox0,
+                   const uint64_t* inbox1, const uint64_t* landing, uint64_t x, uint64_t h, uint64_t trace);
+/* Fills `bytes` bytes at `dptr` with the byte `value`, on the context's stream. */
+int tb200_memset(tb200_ctx* ctx, uint64_t dptr, int value, size_t bytes);
 
 /* No counterpart in the reference. Paged decode attention (the computation of
  * the "decode_attention" kernel above) for callers that cannot allocate device

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SO = os.path.join(HERE, "libtessel_b200.so")
+# TESSEL_B200_LIB selects another build of the same ABI (the trace build of tessel_b200/build.py).
+SO = os.environ.get("TESSEL_B200_LIB") or os.path.join(HERE, "libtessel_b200.so")
 
 # Every symbol include/tessel_b200.h declares: (name, restype, argtypes).
 _u64p = C.POINTER(C.c_uint64)
@@ -47,9 +48,10 @@ SYMBOLS = [
     ("tb200_allreduce", C.c_int, [C.c_void_p, C.c_uint64, C.c_size_t, C.c_int]),
     ("tb200_ipc_export", C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
     ("tb200_ipc_import", C.c_int, [C.c_void_p, C.c_void_p, _u64p]),
-    ("tb200_tp_sizes", C.c_int, [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    ("tb200_tp_sizes", C.c_int, [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     ("tb200_tp_table", C.c_int,
-     [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, _u64p, _u64p, _u64p, _u64p, _u64p, _u64p, C.c_uint64]),
+     [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_int, _u64p, _u64p, _u64p, C.c_uint64, C.c_uint64, C.c_uint64]),
+    ("tb200_memset", C.c_int, [C.c_void_p, C.c_uint64, C.c_int, C.c_size_t]),
     ("tb200_decode_attention_static", C.c_int,
      [C.c_void_p, C.POINTER(C.c_int32), C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
       C.c_float]),

@@ -17,6 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 SO = os.path.join(HERE, "libtessel_b200.so")
+SO_TRACE = os.path.join(HERE, "libtessel_b200_trace.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -38,17 +39,20 @@ def _newest_header() -> float:
     return max(os.path.getmtime(h) for h in hs)
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> str:
-    os.makedirs(OBJ, exist_ok=True)
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, trace: bool = False) -> str:
+    """``trace``: a second library, ``libtessel_b200_trace.so``, whose exchange kernel stamps
+    %globaltimer at its phase boundaries (``-DTB200_TRACE``); select it with TESSEL_B200_LIB."""
+    obj_dir, so = (OBJ + "_trace", SO_TRACE) if trace else (OBJ, SO)
+    os.makedirs(obj_dir, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     hdr = _newest_header()
     jobs = []
     objs = []
     for s in srcs:
-        o = os.path.join(OBJ, os.path.basename(s)[:-3] + ".o")
+        o = os.path.join(obj_dir, os.path.basename(s)[:-3] + ".o")
         objs.append(o)
         if force or not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(s), hdr):
-            cmd = [nvcc(), *NVCC_FLAGS, "-c", s, "-o", o]
+            cmd = [nvcc(), *NVCC_FLAGS, *(["-DTB200_TRACE"] if trace else []), "-c", s, "-o", o]
             if ptxas_info:
                 cmd += ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -64,14 +68,15 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
                     sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
                 if r.returncode != 0:
                     raise RuntimeError("nvcc failed on " + cmd[-3])
-    if jobs or not os.path.exists(SO):
-        link = [nvcc(), "-shared", "-o", SO, *objs, "-ldl", "-gencode", "arch=compute_100a,code=sm_100a"]
+    if jobs or not os.path.exists(so):
+        link = [nvcc(), "-shared", "-o", so, *objs, "-ldl", "-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(link, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    return SO
+    return so
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, ptxas_info="--ptxas" in sys.argv))
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, ptxas_info="--ptxas" in sys.argv,
+                trace="--trace" in sys.argv))

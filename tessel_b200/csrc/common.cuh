@@ -164,16 +164,15 @@ constexpr int TP_MAX = 8;
 // Row r of a step belongs to rank r % n. part[w][o] is owner o's INBOX w: f32
 // [n sources][ceil(T / n) rows][dim], where source s's projection kernel stores its partial of
 // owner o's rows (linear_scatter). stage[o] is rank o's landing area for the other owners'
-// finished rows: 8-byte units {payload | epoch << 32}, [T][dim] units (payload: two halves of h
-// for the first dim / 2 units of a row, or one f32 of x for all dim units on the last call of a
-// step).
+// finished rows: 32-bit words, [T][dim / 2] of two halves of h, or [T][dim] of one f32 of x on
+// the last call of a step. Inboxes and landing areas hold 0xffffffff in every word that is not
+// waiting to be consumed (csrc/tp.cu).
 struct TpTable {
   float* part[2][TP_MAX];
-  float* x[TP_MAX];             // residual stream of every rank
-  __half* h[TP_MAX];            // normalised activations of every rank
-  unsigned long long* stage[TP_MAX];
-  unsigned int* flags[TP_MAX];  // [TP_SLOTS][TP_PHASES][TP_MAX senders]
-  unsigned int* epoch;          // [TP_SLOTS], local: launches this slot has taken part in
+  unsigned int* stage[TP_MAX];
+  float* x;             // this rank's residual stream
+  __half* h;            // this rank's normalised activations
+  unsigned int* trace;  // trace builds only (may be null): call counters and time stamps
   int rank, nranks;
 };
 
@@ -190,10 +189,9 @@ int make_prefill(Ctx* c, Op& op);
 int make_tp(Ctx* c, Op& op);
 int launch_tp(Ctx* c, Op& op, const uint64_t* a);
 size_t tp_table_bytes();
-size_t tp_flag_bytes();
-size_t tp_epoch_bytes();
-int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint64_t* part0, const uint64_t* part1,
-                  const uint64_t* x, const uint64_t* h, const uint64_t* stage, const uint64_t* flags, uint64_t epoch);
+size_t tp_trace_bytes();
+int tp_fill_table(void* out, size_t out_bytes, int rank, int nranks, const uint64_t* inbox0, const uint64_t* inbox1,
+                  const uint64_t* landing, uint64_t x, uint64_t h, uint64_t trace);
 int launch_prefill(Ctx* c, Op& op, const uint64_t* a);
 
 // Launches `kern` on the context's stream, as a cluster of (cluster_x, 1, cluster_z) when that

@@ -609,19 +609,26 @@ int tb200_ipc_import(tb200_ctx* h, const void* handle, uint64_t* dptr) {
   return 0;
 }
 
-int tb200_tp_sizes(size_t* table_bytes, size_t* flag_bytes, size_t* epoch_bytes) {
+int tb200_tp_sizes(size_t* table_bytes, size_t* trace_bytes) {
   if (table_bytes) *table_bytes = tp_table_bytes();
-  if (flag_bytes) *flag_bytes = tp_flag_bytes();
-  if (epoch_bytes) *epoch_bytes = tp_epoch_bytes();
+  if (trace_bytes) *trace_bytes = tp_trace_bytes();
   return 0;
 }
 
-int tb200_tp_table(tb200_ctx* h, void* out, size_t bytes, int rank, int nranks, const uint64_t* part0,
-                   const uint64_t* part1, const uint64_t* x, const uint64_t* hh, const uint64_t* stage,
-                   const uint64_t* flags, uint64_t epoch) {
+int tb200_tp_table(tb200_ctx* h, void* out, size_t bytes, int rank, int nranks, const uint64_t* inbox0,
+                   const uint64_t* inbox1, const uint64_t* landing, uint64_t x, uint64_t hh, uint64_t trace) {
   Ctx* c = &h->c;
-  if (tp_fill_table(out, bytes, rank, nranks, part0, part1, x, hh, stage, flags, epoch))
+  if (tp_fill_table(out, bytes, rank, nranks, inbox0, inbox1, landing, x, hh, trace))
     return fail(c, "tb200_tp_table: 1 to 8 ranks, rank inside, and a buffer of tb200_tp_sizes' table size");
+  return 0;
+}
+
+int tb200_memset(tb200_ctx* h, uint64_t dptr, int value, size_t bytes) {
+  Ctx* c = &h->c;
+  if (c->capturing) return fail(c, "tb200_memset during graph capture");
+  if (bytes == 0) return 0;
+  TB_CUDA(c, cudaSetDevice(c->device));
+  TB_CUDA(c, cudaMemsetAsync((void*)dptr, value, bytes, c->stream));
   return 0;
 }
 

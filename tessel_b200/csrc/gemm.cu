@@ -127,7 +127,9 @@ __device__ __forceinline__ void scatter_store(const GemmParams& p, float* stage,
   float* const* inbox = t->part[p.which];
 #pragma unroll 4
   for (int r = 0; r < 32; ++r) {
-    const float val = stage[r * 32 + (((lane >> 2) ^ (r & 7)) << 2) + (lane & 3)];
+    float val = stage[r * 32 + (((lane >> 2) ^ (r & 7)) << 2) + (lane & 3)];
+    // 0xffffffff marks an empty inbox word (csrc/tp.cu): that NaN goes out as another NaN.
+    if (__float_as_uint(val) == 0xffffffffu) val = __uint_as_float(0x7fffffffu);
     if (row0 + r < p.M && col_ok) inbox[owner][at] = val;
     if (++owner == n) {
       owner = 0;

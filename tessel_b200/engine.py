@@ -220,8 +220,8 @@ class Engine:
         self.mlp = a(t * cfg.ffn * 2)
         self.last = a(t * cfg.dim * 2)
         self.logits = a(t * cfg.vocab * 4)
-        # A rank's partial o_proj / down_proj [t, dim] f32; with the peer-memory exchange, this
-        # rank's inbox: [sources][ceil(t / nranks)][dim], the peers' partials of the rows it owns.
+        # A rank's partial o_proj / down_proj [t, dim] f32 on the NCCL path (sized as an inbox of
+        # the peer-memory exchange, whose tile tuning uses it as a stand-in for the real ones).
         self.part = a((t + nranks) * cfg.dim * 4) if nranks > 1 else None
         self.tok, self.pos, self.slot, self.idx = a(t * 4), a(t * 4), a(t * 4), a(t * 4)
         self.table = a(t * lim.max_seq_pages * 4)
@@ -257,19 +257,30 @@ class Engine:
         # must switch at the same step.
         self.fused = nranks > 1 and exchange is not None
         if nranks > 1 and exchange is not None:
-            _, fb, eb = gpu.tp_sizes()
-            self.part2 = a((t + nranks) * cfg.dim * 4)
-            # Where the other owners' finished rows land: 8-byte units {payload | call counter}.
-            self.tp_stage = a(t * cfg.dim * 8)
-            self.tp_flags, self.tp_epoch = a(fb), a(eb)
-            mine = [self.part, self.part2, self.x, self.h, self.tp_stage, self.tp_flags]
+            # Two inboxes for the projections' partial rows and the landing area for the other
+            # owners' finished rows, every word "empty" (0xffffffff) until something arrives; the
+            # kernels put that back into what they consume. Separate from ``part``, which the
+            # NCCL path fills with partial products.
+            inbox = [a((t + nranks) * cfg.dim * 4), a((t + nranks) * cfg.dim * 4)]
+            self.tp_landing = a(t * cfg.dim * 4)
+            mine = inbox + [self.tp_landing]
+            for b in mine:
+                gpu.fill(b, 0xFF)
+            gpu.sync()  # before any peer may store into them
+            self.tp_trace = a(gpu.tp_sizes()[1])
             everyone = exchange([gpu.ipc_export(b) for b in mine])
             cols = [[] for _ in mine]
             for r in range(nranks):
                 for i, b in enumerate(mine):
                     cols[i].append(b if r == rank else gpu.ipc_import(everyone[r][i], b.bytes))
-            raw = gpu.tp_table(rank, nranks, cols[0], cols[1], cols[2], cols[3], cols[4], cols[5], self.tp_epoch)
+            raw = gpu.tp_table(rank, nranks, cols[0], cols[1], cols[2], self.x, self.h, self.tp_trace)
             self.tp_table = gpu.tensor(np.frombuffer(raw, np.uint8).copy())
+            # Timing the candidate tiles of ``linear_scatter`` must not leave partial rows in the
+            # real inboxes (a word that is not empty counts as arrived): those launches get a
+            # table whose every inbox is this rank's own ``part``.
+            local = [self.part] * nranks
+            raw = gpu.tp_table(rank, nranks, local, local, local, self.x, self.h, None)
+            self.tp_tune_table = gpu.tensor(np.frombuffer(raw, np.uint8).copy())
 
     # -- one step ----------------------------------------------------------------
     def _upload(self, tokens, pos, slots, attn, want):
@@ -519,8 +530,9 @@ class Engine:
             # Each row of a partial product goes straight into its owner rank's inbox.
             from .gpu import I32
             tb = self.tp_table
-            oproj = self._mm("linear_scatter", [[t, nh * hd], [dm, nh * hd], [tb.bytes]], [self.o, l0.wo, tb, I32(0)], t)
-            down = self._mm("linear_scatter", [[t, f], [dm, f], [tb.bytes]], [self.mlp, l0.wd, tb, I32(1)], t)
+            tt = self.tp_tune_table
+            oproj = self._mm("linear_scatter", [[t, nh * hd], [dm, nh * hd], [tb.bytes]], [self.o, l0.wo, tt, I32(0)], t)
+            down = self._mm("linear_scatter", [[t, f], [dm, f], [tb.bytes]], [self.mlp, l0.wd, tt, I32(1)], t)
         else:
             proj = "linear_f32" if tp else "linear_residual"
             acc = self.part if tp else self.x

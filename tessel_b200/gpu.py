@@ -290,19 +290,26 @@ class Gpu:
         return Buf(p.value, nbytes)
 
     def tp_sizes(self):
-        """(table, flags, epochs) byte sizes of the fused cross-rank reduction's bookkeeping."""
-        a, b, c = C.c_size_t(), C.c_size_t(), C.c_size_t()
-        self._check(self._l.tb200_tp_sizes(C.byref(a), C.byref(b), C.byref(c)))
-        return a.value, b.value, c.value
+        """(table, trace) byte sizes of the fused cross-rank reduction's bookkeeping."""
+        a, b = C.c_size_t(), C.c_size_t()
+        self._check(self._l.tb200_tp_sizes(C.byref(a), C.byref(b)))
+        return a.value, b.value
 
-    def tp_table(self, rank: int, nranks: int, part0, part1, x, h, stage, flags, epoch: Buf) -> bytes:
-        """The table ``tp_reduce_norm`` reads: lists of Buf indexed by rank."""
+    def tp_table(self, rank: int, nranks: int, inbox0, inbox1, landing, x: Buf, h: Buf,
+                 trace: Optional[Buf] = None) -> bytes:
+        """The table ``linear_scatter`` and ``tp_reduce_norm`` read. ``inbox0``, ``inbox1`` and
+        ``landing`` are lists of Buf indexed by rank (filled with 0xff bytes by their owners:
+        :meth:`fill`), ``x`` and ``h`` this rank's own buffers."""
         n = self.tp_sizes()[0]
         out = C.create_string_buffer(n)
         arr = lambda bs: (C.c_uint64 * 8)(*[b.ptr for b in bs])
-        self._check(self._l.tb200_tp_table(self._h, out, n, rank, nranks, arr(part0), arr(part1), arr(x), arr(h),
-                                           arr(stage), arr(flags), epoch.ptr))
+        self._check(self._l.tb200_tp_table(self._h, out, n, rank, nranks, arr(inbox0), arr(inbox1), arr(landing),
+                                           x.ptr, h.ptr, trace.ptr if trace else 0))
         return out.raw
+
+    def fill(self, b: Buf, value: int) -> None:
+        """Every byte of ``b`` set to ``value`` (``tb200_memset``, on the stream)."""
+        self._check(self._l.tb200_memset(self._h, b.ptr, value, b.bytes))
 
     def allreduce(self, b: Buf, count: int, dtype: int = 0) -> None:
         self._check(self._l.tb200_allreduce(self._h, b.ptr, count, dtype))

@@ -208,6 +208,26 @@ def qkv_rope(gpu, torch, m=256, k=4096, heads=32, kv_heads=8, dim=128, iters=20,
             "rope_kv_us": r_ms * 1e3}
 
 
+def exchange_timeline(gpu, trace, grid):
+    """The stamps a trace build of the exchange kernel left in the table's trace buffer
+    (tessel_b200/build.py --trace): for the last two calls, thread 0 of each CTA at kernel start
+    (the projection before it on the stream is complete), when the partials of its first row
+    have all landed, when its rows are summed, normalised and sent, and when the other owners'
+    rows have landed. Returns microseconds: medians over the CTAs per phase, the span of the
+    whole launch, and the time from the end of the previous call to the start of the last (the
+    projection between them), or None when the library is not a trace build."""
+    words = gpu.fetch(trace, np.uint32, (trace.bytes // 4,))
+    tail = words[64:].view(np.uint64).reshape(2, 64, 4)[:, :min(grid, 64)]
+    if not tail.all():
+        return None
+    last = int(tail[1, 0, 0] > tail[0, 0, 0])
+    cur, prev = tail[last].astype(np.int64), tail[1 - last].astype(np.int64)
+    us = lambda a: float(np.median(a)) / 1e3
+    return {"partials_landed_us": us(cur[:, 1] - cur[:, 0]), "sum_norm_send_us": us(cur[:, 2] - cur[:, 1]),
+            "gather_us": us(cur[:, 3] - cur[:, 2]), "launch_span_us": float(cur[:, 3].max() - cur[:, 0].min()) / 1e3,
+            "projection_between_calls_us": float(cur[:, 0].min() - prev[:, 3].max()) / 1e3, "ctas": int(cur.shape[0])}
+
+
 def exchange(torch, tokens=256, dim=4096, k_cols=4096, calls=64, reps=10):
     """Per-call device time of the tensor-parallel exchange, replayed as a graph of `calls`
     projection + exchange pairs (what a decode step does `2 x layers` times): the peer-memory
@@ -232,23 +252,28 @@ def exchange(torch, tokens=256, dim=4096, k_cols=4096, calls=64, reps=10):
     wt = torch.empty((dim, kl), dtype=torch.float16, device="cuda").normal_(0, 0.02, generator=gen)
     gain = torch.ones((dim,), dtype=torch.float16, device="cuda")
     tbuf = lambda t: Buf(t.data_ptr(), t.numel() * t.element_size())
-    _, fb, eb = gpu.tp_sizes()
     a = gpu.alloc
-    mine = [a((T + world) * dim * 4), a((T + world) * dim * 4), a(T * dim * 4), a(T * dim * 2), a(T * dim * 8), a(fb)]
+    x, h, trace = a(T * dim * 4), a(T * dim * 2), a(gpu.tp_sizes()[1])
+    mine = [a((T + world) * dim * 4), a((T + world) * dim * 4), a(T * dim * 4)]  # two inboxes, the landing area
+    for b in mine:
+        gpu.fill(b, 0xFF)
+    gpu.sync()
     everyone = [None] * world
     dist.all_gather_object(everyone, [gpu.ipc_export(b) for b in mine])
     cols = [[b if r == rank else gpu.ipc_import(everyone[r][i], b.bytes) for r in range(world)]
             for i, b in enumerate(mine)]
-    raw = gpu.tp_table(rank, world, cols[0], cols[1], cols[2], cols[3], cols[4], cols[5], a(eb))
-    table = gpu.tensor(np.frombuffer(raw, np.uint8).copy())
-    x, h = mine[2], mine[3]
+    table = gpu.tensor(np.frombuffer(gpu.tp_table(rank, world, cols[0], cols[1], cols[2], x, h, trace), np.uint8).copy())
+    # The tile candidates are timed against a stand-in table (every inbox a local buffer), so that
+    # the real inboxes stay empty.
+    stand_in = [a((T + world) * dim * 4)] * world
+    tune_table = gpu.tensor(np.frombuffer(gpu.tp_table(rank, world, stand_in, stand_in, stand_in, x, h), np.uint8).copy())
     part = a(T * dim * 4)
     ks = gpu.kernel("linear_scatter", [[T, kl], [dim, kl], [table.bytes]])
     kt = gpu.kernel("tp_reduce_norm", [[table.bytes], [dim], [T, dim]])
     kf = gpu.kernel("linear_f32", [[T, kl], [dim, kl], [T, dim]])
     kr = gpu.kernel("residual_add", [[T, dim], [T, dim]])
     kn = gpu.kernel("rmsnorm", [[T, dim], [dim], [T, dim]])
-    gpu.tune(ks, [tbuf(xin), tbuf(wt), table, I32(0)])
+    gpu.tune(ks, [tbuf(xin), tbuf(wt), tune_table, I32(0)])
     gpu.tune(kf, [tbuf(xin), tbuf(wt), part])
     eps = F32(1e-5)
 
@@ -284,6 +309,11 @@ def exchange(torch, tokens=256, dim=4096, k_cols=4096, calls=64, reps=10):
         t = torch.tensor([ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         out[name + "_us_per_pair"] = float(t[0]) / (reps * calls) * 1e3
+        if name == "peer_memory":
+            lines = [None] * world
+            dist.all_gather_object(lines, exchange_timeline(gpu, trace, -(-T // world)))
+            if lines[0] is not None:
+                out["timeline_by_rank"] = lines
     # The projection alone, for the difference.
     gpu.capture_begin()
     for _ in range(calls):
