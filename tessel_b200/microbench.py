@@ -110,6 +110,33 @@ def gemm(gpu, torch, m=4096, n=4096, k=4096, kind="matmul", iters=20, seed=0):
         b, c = u(k, n), torch.zeros((m, n), dtype=torch.float16, device="cuda")
         kern, args, nb = gpu.kernel("matmul", [[m, k], [k, n], [m, n]]), [buf(a), buf(b), buf(c)], 1
         out_bytes = 2
+    elif kind in ("linear_q8", "linear_residual_q8", "gate_up_q8"):
+        # FP8 mode: E4M3 bytes (finite codes only) with per-row scales; flops as the f16 kinds, bytes halved.
+        def q(*shape):
+            mag = torch.randint(0, 0x78, shape, dtype=torch.uint8, device="cuda", generator=gen)
+            sign = torch.randint(0, 2, shape, dtype=torch.uint8, device="cuda", generator=gen) * 0x80
+            return mag | sign
+
+        sc = lambda r: torch.full((r,), 1.0 / 448.0, dtype=torch.float32, device="cuda")
+        aq, sa, bq, sb = q(m, k), sc(m), q(n, k), sc(n)
+        f32 = kind == "linear_residual_q8"
+        c = torch.zeros((m, n), dtype=torch.float32 if f32 else torch.float16, device="cuda")
+        if kind == "gate_up_q8":
+            b2q, sb2 = q(n, k), sc(n)
+            kern = gpu.kernel(kind, [[m, k], [m], [n, k], [n], [n, k], [n], [m, n]])
+            args, nb = [buf(aq), buf(sa), buf(bq), buf(sb), buf(b2q), buf(sb2), buf(c)], 2
+        else:
+            kern = gpu.kernel(kind, [[m, k], [m], [n, k], [n], [m, n]])
+            args, nb = [buf(aq), buf(sa), buf(bq), buf(sb), buf(c)], 1
+        t = Timer(gpu, torch)
+        mean, best = t.run(lambda: gpu.launch(kern, args), iters)
+        flops = 2.0 * m * n * k * nb
+        nbytes = 1.0 * (m * k + nb * k * n) + (8 if f32 else 2) * m * n
+        hbm, tf, kindp = _peaks()
+        return {"kernel": kind, "m": m, "n": n, "k": k, "ms": mean, "ms_min": best, "flops": flops,
+                "algorithmic_bytes": nbytes, "tflops": flops / (mean * 1e-3) / 1e12, "gbs": nbytes / (mean * 1e-3) / 1e9,
+                "frac_hbm": nbytes / (mean * 1e-3) / 1e9 / hbm, "peak_kind": kindp,
+                "note": "the tensor peak of record is the f16 one; no FP8 peak is measured on this pool"}
     elif kind == "gate_up":
         b, b2 = u(n, k, scale=0.05), u(n, k, scale=0.05)
         c = torch.zeros((m, n), dtype=torch.float16, device="cuda")
