@@ -989,8 +989,11 @@ int dispatch(Ctx* c, Op& op, Kind kind, int mt, int bn, const GemmShape& g, int 
              const void* B2, void* out, bool attr_only) {
   if (mt == PAIR) {
     if (kind == K_MATMUL) return fail(c, "gemm: CTA pairs take K-major weights only");
+    if (bn == 64) return dispatch_pair<64>(c, op, kind, g, splits, A, B, B2, out, attr_only);
+    if (bn == 96) return dispatch_pair<96>(c, op, kind, g, splits, A, B, B2, out, attr_only);
     if (bn == 128) return dispatch_pair<128>(c, op, kind, g, splits, A, B, B2, out, attr_only);
     if (bn == 192) return dispatch_pair<192>(c, op, kind, g, splits, A, B, B2, out, attr_only);
+    if (bn == 224) return dispatch_pair<224>(c, op, kind, g, splits, A, B, B2, out, attr_only);
     if (bn == 256) return dispatch_pair<256>(c, op, kind, g, splits, A, B, B2, out, attr_only);
     return fail(c, "gemm: no such pair tile");
   }
@@ -1029,7 +1032,8 @@ const char* plan_error(Kind kind, const GemmShape& g, int mt, int bn, int s) {
   };
   if (mt == PAIR) {
     if (kind == K_MATMUL) return "CTA pairs take K-major weights only";
-    if (bn != 128 && bn != 192 && bn != 256) return "pair tiles are 128, 192 or 256 columns wide";
+    if (bn != 64 && bn != 96 && bn != 128 && bn != 192 && bn != 224 && bn != 256)
+      return "pair tiles are 64, 96, 128, 192, 224 or 256 columns wide";
     const int nops = epi == EPI_GATE_UP ? 2 : 1;
     const int stage = BM * BK * 2 + nops * (bn / 2) * BK * 2;
     int stages = (196 * 1024) / stage;
@@ -1108,20 +1112,26 @@ std::vector<Plan> plan_gemm(Kind kind, const GemmShape& g, int sms) {
   // eight (a pair times four splits) measured 40-50 % slower than two splits at every decode
   // shape, so they are left to a forced plan.
   if ((g.q8 || (g.M > BM && g.M <= 2 * BM)) && kind != K_MATMUL) {
-    for (int bn : {256, 192, 128}) {
+    // A streaming kernel draws about 44 GB/s per SM (148 of them make the HBM peak), so a plan
+    // is also bounded by the SMs it occupies: hence the tiles between the powers of two (64
+    // pairs of 224 gate_up columns against 56 of 256; 64 pairs of 96 QKV columns).
+    const double SM_FEED = 44e9;
+    for (int bn : {256, 224, 192, 128, 96, 64}) {
       for (int s = 1; s <= 2; s *= 2) {
         if (plan_error(kind, g, PAIR, bn, s)) continue;
         if (s > 1 && nk < 8 * s) continue;
         const int stage = BM * BK * 2 + nbf * (bn / 2) * BK * 2;
         const long long ctas = 2LL * ((g.M + 2 * BM - 1) / (2 * BM)) * ((g.N + bn - 1) / bn) * s;
         const long long waves = (ctas + sms - 1) / sms;
+        if (waves > 1 && bn < 128) continue;  // narrow tiles only where they fill one wave
         const double kiter = (double)((nk + s - 1) / s);
         const double t_feed = kiter * stage / FEED;
         const double t_mma = kiter * (2.0 * BM * nbf * bn * BK) / TENSOR;
         double t_epi = (double)BM * bn * out_bytes / FEED;
         if (s > 1) t_epi += 2.0e-6 + 2.0 * (s - 1) / s * BM * bn * 4 / FEED;
         double t = waves * ((t_feed > t_mma ? t_feed : t_mma) + 2.0e-6 + t_epi);
-        const double floor_t = (2.0 * g.M * g.K + 2.0 * nbf * (double)g.N * g.K + (double)out_bytes * g.M * g.N) / HBM;
+        const double dram = 2.0 * g.M * g.K + 2.0 * nbf * (double)g.N * g.K + (double)out_bytes * g.M * g.N;
+        const double floor_t = dram / ((ctas < sms ? ctas : sms) * SM_FEED);
         if (t < floor_t) t = floor_t;
         all.push_back({PAIR, bn, s, t});
       }

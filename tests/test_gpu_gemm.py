@@ -105,6 +105,8 @@ def test_matmul_4096_cubed(gpu):
     ("3,256,1", 256, 784, 1048), ("3,128,1", 200, 400, 1032), ("3,192,1", 129, 584, 520),
     ("3,256,2", 256, 1304, 2056), ("3,192,2", 256, 6152, 4096), ("3,256,4", 250, 4112, 4104),
     ("3,128,4", 256, 272, 2048), ("3,256,1", 600, 528, 512), ("3,128,2", 1000, 136, 1096),
+    # the pair tiles between the powers of two (they put a projection on more SMs in one wave)
+    ("3,224,1", 256, 1000, 1056), ("3,96,1", 256, 6144, 1064), ("3,64,1", 200, 328, 1072), ("3,64,2", 256, 392, 2064),
 ])
 def test_forced_tiles_and_cluster_split_k(gpu, plan, M, N, K, monkeypatch):
     """Every tile shape, the CTA-pair kernel and the cluster split-K exchange (TB200_GEMM_PLAN = MT,BN,splits), on shapes

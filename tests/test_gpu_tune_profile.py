@@ -23,14 +23,14 @@ def test_tuning_picks_a_tile_and_keeps_the_result(gpu):
         by = gpu.tensor(out0)
         k = gpu.kernel(name, [[M, K], [N, K], [M, N]])
         plan, us = gpu.tune(k, [bx, bw, by])
-        assert plan[0] in (1, 2, 3) and plan[1] in (32, 64, 128, 192, 256) and 1 <= plan[2] <= 4, plan
+        assert plan[0] in (1, 2, 3) and plan[1] in (32, 64, 96, 128, 192, 224, 256) and 1 <= plan[2] <= 4, plan
         assert 1.0 < us < 1000.0, us
         gpu.write(by, 0, out0)  # tuning clobbered (or accumulated into) the output
         gpu.launch(k, [bx, bw, by])
         gpu.sync()
         assert rel_err(gpu.fetch(by, out0.dtype, (M, N)), want) <= 2e-3
         assert gpu.tune(k, [bx, bw, by])[0] in [(1, b, s) for b in (32, 64, 128, 256) for s in (1, 2, 4)] + \
-            [(2, b, s) for b in (32, 64, 128, 192, 256) for s in (1, 2, 4)] + [(3, b, s) for b in (128, 192, 256) for s in (1, 2)]
+            [(2, b, s) for b in (32, 64, 128, 192, 256) for s in (1, 2, 4)] + [(3, b, s) for b in (64, 96, 128, 192, 224, 256) for s in (1, 2)]
     # A kernel without tile candidates: nothing to tune, no error.
     a = gpu.tensor(np.ones((4, 8), f))
     k = gpu.kernel("residual_add", [[4, 8], [4, 8]])
