@@ -235,7 +235,8 @@ int tb200_ipc_import(tb200_ctx* ctx, const void* handle, uint64_t* dptr);
 int tb200_tp_sizes(size_t* table_bytes, size_t* trace_bytes);
 int tb200_tp_table(tb200_ctx* ctx, void* host_out, size_t bytes, int rank, int nranks, const uint64_t* inbox0,
                    const uint64_t* inbox1, const uint64_t* landing, uint64_t x, uint64_t h, uint64_t trace);
-/* Fills `bytes` bytes at `dptr` with the byte `value`, on the context's stream. */
+/* Fills `bytes` bytes at `dptr` with the byte `value`, on the context's stream;
+ * bounds-checked like tb200_write. */
 int tb200_memset(tb200_ctx* ctx, uint64_t dptr, int value, size_t bytes);
 
 /* No counterpart in the reference. Paged decode attention (the computation of

@@ -626,6 +626,7 @@ int tb200_tp_table(tb200_ctx* h, void* out, size_t bytes, int rank, int nranks, 
 int tb200_memset(tb200_ctx* h, uint64_t dptr, int value, size_t bytes) {
   Ctx* c = &h->c;
   if (c->capturing) return fail(c, "tb200_memset during graph capture");
+  if (check_range(c, "memset", dptr, 0, bytes)) return 1;
   if (bytes == 0) return 0;
   TB_CUDA(c, cudaSetDevice(c->device));
   TB_CUDA(c, cudaMemsetAsync((void*)dptr, value, bytes, c->stream));
